@@ -1,0 +1,382 @@
+#!/usr/bin/env python
+"""Benchmark of the fused disentangled-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c5f|c5v]
+
+A step is one pass of the fused attention over one batch of synthetic input (default: configuration 2, bf16,
+batch 32 x seq 512, 12 heads x 64, valid lengths uniform in [64, 512], right padded).  The metric is algorithmic
+TFLOP/s: (4 L^2 d + 4 L R d) per sequence and head, R = min(2*span, 2L-1), summed over the valid lengths, divided by
+the device time of the step.  Under torchrun every rank runs its own batch (weak scaling, no data-path
+collective); the value is the sum of the ranks' work over the slowest rank's time.
+
+One JSON line is printed by rank 0.  `value` is measured with Q, K, V and the tables resident in HBM;
+`e2e` is the same metric through the public Python op with pinned host buffers, host<->device copies included.
+`--impl reference` times the reference's own CPU path (the eager module it subclasses) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "disentangled_attn_algorithmic_tflops"
+UNIT = "TFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on the default workload,
+# from the ncu capture summarised in profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_BYTES = None
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5f", "c5v", "c2full"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "umma"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def make_workload(name: str, rank: int):
+    import numpy as np
+    from turbodeberta_b200 import workloads
+    if name == "c2":
+        return workloads.config2(seed=1002 + rank)
+    if name == "c2full":
+        w = workloads.config2(seed=1002 + rank)
+        w.lengths = np.full_like(w.lengths, 512)
+        w.name = "c2_base_bf16_b32_l512_allvalid"
+        return w
+    if name == "c3":
+        return workloads.config3(seed=1003 + rank)
+    if name == "c5f":
+        return workloads.config5_fixed(seed=1005 + rank)
+    return workloads.config5_varlen(seed=1005 + rank)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_tflops": p["bf16_tflops"], "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------- reference arm
+
+def _eager_step_fns(sample):
+    """(module forward, QKV-projection-only forward) for the eager CPU path.  The metric counts the attention
+    proper (the GPU arm starts from projected Q, K, V), so the projections are timed alone and subtracted."""
+    import torch
+    from oracle import hf_eager
+    mod = hf_eager.build_attention_module(sample)
+    if sample.padded_len is None:
+        full = lambda: hf_eager.attention_module_forward_packed(sample)
+    else:
+        full = lambda: hf_eager.attention_module_forward(sample, module=mod)
+    x = sample.hidden.float()
+
+    @torch.no_grad()
+    def proj():
+        return mod.query_proj(x), mod.key_proj(x), mod.value_proj(x)
+    return full, proj
+
+
+def _time_fn(fn, reps):
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    return (time.perf_counter() - t0) / reps
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path: the eager DisentangledSelfAttention it subclasses
+    (src/turbodeberta/model.py:30), fp32, all host threads, on a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    from oracle import hf_eager
+    w = make_workload(args.workload, 0)
+    n_sample = min(2, len(w.lengths))
+    sample, desc = _cpu_sample(w, n_sample)
+    threads = torch.get_num_threads()
+    full, proj = _eager_step_fns(sample)
+    for _ in range(max(1, min(args.warmup, 2))):
+        full(); proj()
+    steps = max(1, args.steps)
+    t_full = _time_fn(full, steps)
+    t_proj = _time_fn(proj, steps)
+    dt = max(t_full - t_proj, 1e-9)
+    desc += f"; module {t_full * 1e3:.1f} ms minus QKV projections {t_proj * 1e3:.1f} ms"
+    val = sample.flops() / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "sample": desc},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "reference", "sample": desc},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def _cpu_sample(w, n):
+    """First n sequences of the workload as their own (padded or packed) workload, plus a description."""
+    import copy
+    import numpy as np
+    s = copy.copy(w)
+    s.lengths = np.asarray(w.lengths[:n])
+    if w.padded_len is None:
+        s.hidden = w.hidden[: int(s.lengths.sum())]
+    else:
+        s.hidden = w.hidden[:n]
+    s.name = w.name + f"[first {n} sequences]"
+    desc = f"first {n} sequences of {w.name} (lengths {s.lengths.tolist()}), eager attention module, fp32"
+    return s, desc
+
+
+def cpu_baseline(w, budget_s=12.0):
+    import torch
+    from oracle import hf_eager
+    sample, desc = _cpu_sample(w, min(2, len(w.lengths)))
+    try:
+        full, proj = _eager_step_fns(sample)
+        full(); proj()
+        one = _time_fn(full, 1)
+        n = int(max(1, min(20, budget_s / max(one, 1e-3))))
+        t_full = _time_fn(full, n)
+        t_proj = _time_fn(proj, n)
+        dt = max(t_full - t_proj, 1e-9)
+        return {"value": sample.flops() / dt / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
+                "kind": "reference", "sample": desc + f"; {n} repetitions, module {t_full * 1e3:.1f} ms minus QKV "
+                f"projections {t_proj * 1e3:.1f} ms"}
+    except Exception as e:  # transformers missing or incompatible: time the numpy port instead
+        import numpy as np
+        from oracle import disentangled_oracle as orc
+        t0 = time.perf_counter()
+        orc.self_attention_layer(sample.hidden.numpy(), sample.lengths, {k: v.numpy() for k, v in sample.params.items()},
+                                 num_heads=sample.num_heads, position_buckets=sample.position_buckets,
+                                 max_relative_positions=sample.max_relative_positions,
+                                 rel_embeddings=sample.rel_embeddings.numpy())
+        dt = time.perf_counter() - t0
+        return {"value": sample.flops() / dt / 1e12, "unit": UNIT, "cores": 1, "kind": "port",
+                "sample": desc + f" (numpy port; eager module unavailable: {type(e).__name__})"}
+
+
+# ----------------------------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from turbodeberta_b200 import _cabi as cabi
+    from turbodeberta_b200 import relpos, workloads
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    w = make_workload(args.workload, rank)
+    kernel = {"auto": cabi.TDB_KERNEL_AUTO, "simt": cabi.TDB_KERNEL_SIMT, "umma": cabi.TDB_KERNEL_UMMA}[args.kernel]
+    dtype = torch.bfloat16
+    q, k, v = workloads.project_qkv(w, device=dev, dtype=dtype)
+    rel = w.rel_embeddings.to(dev, dtype)
+    P = {n: t.to(dev, dtype) for n, t in w.params.items()}
+    tables = relpos.build_tables(rel, num_heads=w.num_heads, position_buckets=w.position_buckets,
+                                 max_relative_positions=w.max_relative_positions,
+                                 key_weight=P["key_proj.weight"], key_bias=P["key_proj.bias"],
+                                 query_weight=P["query_proj.weight"], query_bias=P["query_proj.bias"])
+    scale = 1.0 / (3 * w.head_dim) ** 0.5
+    fixed = w.padded_len is not None
+    if fixed:
+        lens = torch.as_tensor(np.asarray(w.lengths), dtype=torch.int32, device=dev)
+        qp, kp, vp = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+
+        def step(qq=qp, kk=kp, vv=vp):
+            return flash_attention_with_disentangled(qq, kk, vv, None, None, False, scale, w.position_buckets,
+                                                     w.max_relative_positions, seqlens=lens, tables=tables,
+                                                     kernel=kernel, check_status=False)
+        launches_per_step = 1
+    else:
+        cu = torch.as_tensor(w.cu_seqlens, device=dev)
+        mx = int(w.lengths.max())
+
+        def step(qq=q, kk=k, vv=v):
+            return flash_attention_with_disentangled_varlen(qq, kk, vv, None, None, cu, cu, mx, mx, False, scale,
+                                                            w.position_buckets, w.max_relative_positions,
+                                                            tables=tables, kernel=kernel, check_status=False)
+        launches_per_step = 2      # tile-list kernel + attention kernel
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)    # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        flush.zero_()
+        o = step()
+    torch.cuda.synchronize()
+    # sanity: the output of the timed call is finite on valid rows
+    assert torch.isfinite(o.float()).all(), "attention output is not finite"
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    barrier()
+    evs = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); step(); e1.record()
+        evs.append((e0, e1))
+    barrier()
+    times = [a.elapsed_time(b) for a, b in evs]
+    total_ms = float(sum(times))
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end to end through the public op: pinned host buffers in, host buffer out ----
+    e2e_ms = None
+    h2d = d2h = 0
+    if not args.no_e2e:
+        hq, hk, hv = (t.contiguous().cpu().pin_memory() for t in (q, k, v))
+        hout = torch.empty(q.shape, dtype=dtype).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+        d2h = hout.numel() * hout.element_size()
+
+        def e2e_step():
+            dq, dk, dv = (t.to(dev, non_blocking=True) for t in (hq, hk, hv))
+            if fixed:
+                oo = step(dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)).permute(0, 2, 1, 3)
+            else:
+                oo = step(dq, dk, dv)
+            hout.copy_(oo, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        n_e2e = max(3, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / n_e2e
+
+    flops = w.flops()
+    stats = torch.tensor([total_ms, flops, e2e_ms or 0.0], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx_t = stats.clone(); dist.all_reduce(mx_t, op=dist.ReduceOp.MAX)
+        sm_t = stats.clone(); dist.all_reduce(sm_t, op=dist.ReduceOp.SUM)
+        total_ms, flops_all, e2e_max = float(mx_t[0]), float(sm_t[1]), float(mx_t[2])
+    else:
+        flops_all, e2e_max = flops, e2e_ms or 0.0
+    status_ok = True
+
+    if rank == 0:
+        pk = peaks()
+        ms_per_step = total_ms / args.steps
+        value = flops_all / (ms_per_step * 1e-3) / 1e12
+        kern_tflops = flops / (float(sum(times)) / args.steps * 1e-3) / 1e12      # this rank's kernel alone
+        bytes_alg = w.bytes(2)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w.name, "heads": w.num_heads, "head_dim": w.head_dim, "sequences_per_gpu": len(w.lengths),
+                       "valid_tokens_per_gpu": int(np.sum(w.lengths)), "position_buckets": w.position_buckets,
+                       "max_relative_positions": w.max_relative_positions, "kernel": args.kernel,
+                       "l2": "256 MiB buffer rewritten between timed steps", "parallelism": f"replicas x{world}"},
+            "roofline": {"bound": "tensor", "achieved": kern_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": kern_tflops / pk["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,
+                         "peak_source": pk["source"] + " (burst)", "algorithmic_flops_per_launch": flops,
+                         "algorithmic_bytes_per_launch": bytes_alg,
+                         "hbm_floor_ms": bytes_alg / (pk["hbm_gbs"] * 1e9) * 1e3},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if e2e_ms is not None:
+            line["e2e"] = {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_max,
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -1,0 +1,107 @@
+"""GPU parity of the tensor-core (tcgen05) attention kernel against the oracle, bf16."""
+import numpy as np
+import pytest
+import torch
+
+from tests import util
+from turbodeberta_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+UMMA, SIMT = 2, 1
+DT = torch.bfloat16
+
+
+def _fixed(w, c2p=True, p2c=True, with_lens=True, kernel=UMMA):
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P, c2p, p2c) if (c2p or p2c) else None
+    scale = 1.0 / (w.head_dim * (1 + int(c2p) + int(p2c))) ** 0.5
+    lens = torch.as_tensor(np.asarray(w.lengths), dtype=torch.int32, device="cuda") if with_lens else None
+    o = flash_attention_with_disentangled(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                          None, None, False, scale, w.position_buckets, w.max_relative_positions,
+                                          seqlens=lens, tables=tables, kernel=kernel)
+    ref = util.oracle_fixed(q, k, v, tables, w.lengths if with_lens else None, w, c2p, p2c, scale)
+    return o.permute(0, 2, 1, 3), ref
+
+
+def _wl(lengths, padded, hidden=128, heads=2, seed=31, buckets=256, maxpos=512):
+    return workloads.make_attention_workload("t", seed=seed, hidden_size=hidden, num_heads=heads, lengths=lengths,
+                                             padded_len=padded, position_buckets=buckets,
+                                             max_relative_positions=maxpos, dtype=DT)
+
+
+def test_umma_content_only_one_tile():
+    o, ref = _fixed(_wl([128], 128, hidden=64, heads=1), c2p=False, p2c=False, with_lens=False)
+    util.assert_close(o, ref, DT, "QK^T/softmax/PV only, one tile")
+
+
+def test_umma_content_only_multi_tile():
+    o, ref = _fixed(_wl([384, 300], 384), c2p=False, p2c=False)
+    util.assert_close(o, ref, DT, "content only, 3 key tiles, padded")
+
+
+def test_umma_c2p_only():
+    o, ref = _fixed(_wl([256, 200], 256), c2p=True, p2c=False)
+    util.assert_close(o, ref, DT, "c2p only")
+
+
+def test_umma_p2c_only():
+    o, ref = _fixed(_wl([256, 200], 256), c2p=False, p2c=True)
+    util.assert_close(o, ref, DT, "p2c only")
+
+
+@pytest.mark.parametrize("lengths,padded", [([128], 128), ([512, 64, 333, 129], 512), ([700, 1], 700), ([40, 23], 40)])
+def test_umma_both_terms_fixed(lengths, padded):
+    o, ref = _fixed(_wl(lengths, padded))
+    util.assert_close(o, ref, DT, f"fixed {lengths}")
+
+
+def test_umma_all_ones_no_lengths():
+    o, ref = _fixed(_wl([256, 256, 256], 256, hidden=192, heads=3), with_lens=False)
+    util.assert_close(o, ref, DT, "all ones")
+
+
+@pytest.mark.parametrize("pair", [(32, 64), (0, 64), (64, 128)])
+def test_umma_other_bucket_geometries(pair):
+    o, ref = _fixed(_wl([300, 257], 300, buckets=pair[0], maxpos=pair[1]))
+    util.assert_close(o, ref, DT, f"buckets {pair}")
+
+
+def test_umma_matches_simt_closely():
+    """Both kernels see identical bf16 inputs; they must agree much more tightly than the oracle tolerance."""
+    w = _wl([512, 384], 512, hidden=256, heads=4)
+    o1, _ = _fixed(w, kernel=UMMA)
+    o2, _ = _fixed(w, kernel=SIMT)
+    assert (o1.float() - o2.float()).abs().max().item() < 1e-2
+
+
+def test_umma_varlen():
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+    lengths = [5, 1, 33, 17, 128, 129, 127, 600, 16, 15, 1100]
+    w = _wl(lengths, None)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    cu = torch.as_tensor(w.cu_seqlens, device="cuda")
+    scale = 1.0 / (3 * 64) ** 0.5
+    o, lse = flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, 1100, 1100, False, scale, 256, 512,
+                                                      tables=tables, kernel=UMMA, return_lse=True)
+    ref = util.oracle_varlen(q, k, v, tables, w.cu_seqlens, w, sm_scale=scale)
+    util.assert_close(o, ref, DT, "varlen")
+    o2, lse2 = flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, 1100, 1100, False, scale, 256, 512,
+                                                        tables=tables, kernel=SIMT, return_lse=True)
+    assert (lse - lse2).abs().max().item() < 5e-2
+    # running the same launch twice must give bit-identical results (no races)
+    o3 = flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, 1100, 1100, False, scale, 256, 512,
+                                                  tables=tables, kernel=UMMA)
+    assert torch.equal(o, o3)
+
+
+def test_umma_bad_cu_seqlens_reported():
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+    w = _wl([64, 64], None)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    cu = torch.tensor([0, 80, 64], dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError):
+        flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, 64, 64, False, 0.07, 256, 512,
+                                                 tables=tables, kernel=UMMA)
