@@ -120,6 +120,34 @@ TDB_API int tdb_attn_fwd_varlen(const void* q, const void* k, const void* v, voi
                         void* workspace, size_t workspace_bytes,
                         float* lse, int32_t* status, void* stream);
 
+/* Packed-form attention for callers that cannot provide scratch memory.  No counterpart in the reference.
+ *
+ * Some hosts of this library cannot allocate device memory at the point where they call it: an inference
+ * server's execute callback that is handed only its bound input and output buffers, or a C/C++ program that has
+ * given all device memory to a framework's pool and holds no handle to that pool.  tdb_attn_fwd_varlen needs a
+ * caller-provided workspace for its device-built tile list; this variant keeps that list in a fixed array that
+ * lives inside the library image on the device (TDB_STATIC_SCRATCH_BYTES, held by every GPU that loads the
+ * library until the process exits) and therefore takes no workspace arguments.  It calls no allocator.
+ *
+ * Limit: tdb_attn_workspace_bytes(n_seqs, total_tokens) must not exceed TDB_STATIC_SCRATCH_BYTES, i.e.
+ * n_seqs + ceil(total_tokens / 128) + 1 <= TDB_STATIC_MAX_TILES; larger problems return TDB_ERR_WORKSPACE.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first
+ * call outside any stream capture.  All calls on a device share the one array and it keeps the previous call's
+ * contents (each call rewrites the part it reads, nothing has to start at zero), so two calls whose kernels can
+ * overlap on the GPU -- different streams, or different host threads -- race on it: serialise them.
+ * All other arguments are those of tdb_attn_fwd_varlen. */
+#define TDB_STATIC_MAX_TILES 65535
+#define TDB_STATIC_SCRATCH_BYTES (16 + 8 * TDB_STATIC_MAX_TILES)
+TDB_API int tdb_attn_fwd_varlen_static(const void* q, const void* k, const void* v, void* o,
+                        int64_t q_st, int64_t q_sh, int64_t k_st, int64_t k_sh,
+                        int64_t v_st, int64_t v_sh, int64_t o_st, int64_t o_sh,
+                        const void* kr, const void* qr, int two_span,
+                        const int16_t* idx, int idx_delta_max,
+                        const void* kr_exp, const void* qr_exp, int exp_delta_max, int exp_rows,
+                        const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, int max_seqlen,
+                        int H, int D, float sm_scale, int flags, int dtype, int kernel,
+                        float* lse, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

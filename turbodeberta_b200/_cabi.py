@@ -17,10 +17,13 @@ TDB_DTYPE_F32, TDB_DTYPE_BF16 = 0, 1
 TDB_FLAG_C2P, TDB_FLAG_P2C = 1, 2
 TDB_KERNEL_AUTO, TDB_KERNEL_SIMT, TDB_KERNEL_UMMA = 0, 1, 2
 TDB_EXPAND_MARGIN = 256
+TDB_STATIC_MAX_TILES = 65535
+TDB_STATIC_SCRATCH_BYTES = 16 + 8 * TDB_STATIC_MAX_TILES
 ERR_ARG, ERR_DTYPE, ERR_ALIGN, ERR_SHAPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = range(-1, -9, -1)
 
 EXPORTS = ["tdb_version", "tdb_strerror", "tdb_last_error", "tdb_bucket_table", "tdb_relpos_project",
-           "tdb_relpos_expand", "tdb_attn_workspace_bytes", "tdb_attn_fwd_fixed", "tdb_attn_fwd_varlen"]
+           "tdb_relpos_expand", "tdb_attn_workspace_bytes", "tdb_attn_fwd_fixed", "tdb_attn_fwd_varlen",
+           "tdb_attn_fwd_varlen_static"]
 
 
 class TdbError(RuntimeError):
@@ -54,6 +57,9 @@ def _load() -> C.CDLL:
     lib.tdb_attn_fwd_varlen.restype = i32
     lib.tdb_attn_fwd_varlen.argtypes = ([vp] * 4 + [i64] * 8 + [vp, vp, i32, vp, i32, vp, vp, i32, i32]
                                         + [vp, i32, i64, i32, i32, i32, f32, i32, i32, i32, vp, sz, vp, vp, vp])
+    lib.tdb_attn_fwd_varlen_static.restype = i32
+    lib.tdb_attn_fwd_varlen_static.argtypes = ([vp] * 4 + [i64] * 8 + [vp, vp, i32, vp, i32, vp, vp, i32, i32]
+                                               + [vp, i32, i64, i32, i32, i32, f32, i32, i32, i32, vp, vp, vp])
     return lib
 
 

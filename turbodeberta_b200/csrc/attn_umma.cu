@@ -25,6 +25,7 @@
 #include "ptx_sm100.cuh"
 #include <cudaTypedefs.h>
 #include <math_constants.h>
+#include <mutex>
 
 namespace tdb {
 using namespace ptx;
@@ -470,6 +471,31 @@ int launch_variant(const AttnParams& p, dim3 grid, const CUtensorMap* maps, cuda
 }
 
 }  // namespace
+
+// Fixed tile-list storage for tdb_attn_fwd_varlen_static: lives in the library image on every device that loads
+// it.  In host code the name below is only a stand-in for the symbol, not a device address; the address comes
+// from cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char g_static_tile_scratch[TDB_STATIC_SCRATCH_BYTES];
+
+int static_tile_scratch(void** ptr) {
+  constexpr int MAX_DEV = 64;
+  static void* addr[MAX_DEV] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= MAX_DEV) { set_error("device ordinal %d out of range", dev); return TDB_ERR_UNSUPPORTED; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_tile_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static tile scratch)");
+    if (!p) { set_error("cudaGetSymbolAddress returned a null address"); return TDB_ERR_CUDA; }
+    addr[dev] = p;
+  }
+  *ptr = addr[dev];
+  return TDB_OK;
+}
 
 size_t umma_workspace_bytes(int n_seqs, int64_t total_tokens) {
   int64_t cap = (total_tokens + BQ - 1) / BQ + n_seqs + 1;

@@ -202,4 +202,30 @@ TDB_API int tdb_attn_fwd_varlen(const void* q, const void* k, const void* v, voi
   return launch_attn_umma(p, (cudaStream_t)stream);
 }
 
+// Same as tdb_attn_fwd_varlen, with the tile list kept in the library's fixed device array instead of a
+// caller-provided workspace.  Allocates nothing; the first call on a device resolves the array's address.
+TDB_API int tdb_attn_fwd_varlen_static(const void* q, const void* k, const void* v, void* o,
+                        int64_t q_st, int64_t q_sh, int64_t k_st, int64_t k_sh, int64_t v_st, int64_t v_sh,
+                        int64_t o_st, int64_t o_sh, const void* kr, const void* qr, int two_span,
+                        const int16_t* idx, int idx_delta_max, const void* kr_exp, const void* qr_exp,
+                        int exp_delta_max, int exp_rows, const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens,
+                        int max_seqlen, int H, int D, float sm_scale, int flags, int dtype, int kernel,
+                        float* lse, int32_t* status, void* stream) {
+  if (n_seqs < 0 || total_tokens < 0) { set_error("negative size"); return TDB_ERR_ARG; }
+  const size_t need = umma_workspace_bytes(n_seqs, total_tokens);
+  if (need > (size_t)TDB_STATIC_SCRATCH_BYTES) {
+    set_error("problem needs %zu bytes of tile list but the built-in scratch holds %zu "
+              "(limit: n_seqs + ceil(total_tokens/128) + 1 <= %d); use tdb_attn_fwd_varlen with a workspace",
+              need, (size_t)TDB_STATIC_SCRATCH_BYTES, TDB_STATIC_MAX_TILES);
+    return TDB_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  int rc = static_tile_scratch(&scratch);
+  if (rc) return rc;
+  return tdb_attn_fwd_varlen(q, k, v, o, q_st, q_sh, k_st, k_sh, v_st, v_sh, o_st, o_sh, kr, qr, two_span, idx,
+                             idx_delta_max, kr_exp, qr_exp, exp_delta_max, exp_rows, cu_seqlens, n_seqs, total_tokens,
+                             max_seqlen, H, D, sm_scale, flags, dtype, kernel, scratch, (size_t)TDB_STATIC_SCRATCH_BYTES,
+                             lse, status, stream);
+}
+
 }  // extern "C"

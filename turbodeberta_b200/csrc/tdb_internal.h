@@ -46,5 +46,6 @@ int launch_relpos_expand(const void* table, const int16_t* idx, int idx_delta_ma
 int launch_attn_simt(const AttnParams& p, int dtype, cudaStream_t s);
 int launch_attn_umma(const AttnParams& p, cudaStream_t s);
 size_t umma_workspace_bytes(int n_seqs, int64_t total_tokens);
+int static_tile_scratch(void** ptr);   // device address of the library's fixed tile-list array on the current device
 
 }  // namespace tdb
