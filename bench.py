@@ -29,8 +29,8 @@ sys.path.insert(0, ROOT)
 METRIC = "disentangled_attn_algorithmic_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on the default workload,
-# from the ncu capture summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES = None
+# from the ncu capture summarised in profiles/attn_umma_config2.md.
+NCU_TRAFFIC_BYTES = 59.94e6     # profiles/attn_umma_config2.md: 56.31 MB read + 3.63 MB written
 
 
 def parse():
