@@ -1,0 +1,106 @@
+"""GPU parity of the patched HF modules against the eager modules they replace."""
+import numpy as np
+import pytest
+import torch
+
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _cfg(**kw):
+    from transformers import DebertaV2Config
+    base = dict(vocab_size=500, hidden_size=128, num_hidden_layers=2, num_attention_heads=2, intermediate_size=256,
+                relative_attention=True, position_buckets=256, max_relative_positions=-1, norm_rel_ebd="layer_norm",
+                share_att_key=True, pos_att_type=["p2c", "c2p"], position_biased_input=False, type_vocab_size=0,
+                hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    base.update(kw)
+    return DebertaV2Config(**base)
+
+
+def _ext(mask2d):
+    e = mask2d[:, None, None, :]
+    return e * e.squeeze(-2).unsqueeze(-1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mask_kind", ["ones", "right", "left"])
+@pytest.mark.parametrize("share,pos", [(True, ["c2p", "p2c"]), (False, ["c2p", "p2c"]), (True, ["c2p"]), (True, [])])
+def test_attention_module_matches_eager(dtype, mask_kind, share, pos):
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DisentangledSelfAttention
+    from turbodeberta_b200.model import FlashDisentangledSelfAttention
+    torch.manual_seed(3)
+    cfg = _cfg(share_att_key=share, pos_att_type=pos, relative_attention=len(pos) > 0)
+    ref = DisentangledSelfAttention(cfg).eval()
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.normal_(0, 0.05)
+    B, L = 3, 200
+    x = torch.randn(B, L, 128)
+    rel = torch.randn(512, 128) * 0.1
+    lens = {"ones": [L, L, L], "right": [200, 37, 129], "left": [200, 37, 129]}[mask_kind]
+    m = torch.zeros(B, L, dtype=torch.long)
+    for b, n in enumerate(lens):
+        if mask_kind == "left":
+            m[b, L - n:] = 1
+        else:
+            m[b, :n] = 1
+    # reference: fp32 eager on the same (dtype-rounded) parameters and inputs
+    ref_r = DisentangledSelfAttention(cfg).eval()
+    ref_r.load_state_dict({k: v.to(dtype).float() for k, v in ref.state_dict().items()})
+    xr, relr = x.to(dtype).float(), rel.to(dtype).float()
+    with torch.no_grad():
+        want, _ = ref_r(xr, _ext(m).bool(), relative_pos=None, rel_embeddings=relr)
+    fl = FlashDisentangledSelfAttention(cfg).eval()
+    fl.load_state_dict(ref.state_dict())
+    fl = fl.to("cuda", dtype)
+    with torch.no_grad():
+        got, probs = fl(x.to("cuda", dtype), _ext(m).to("cuda"), rel_embeddings=rel.to("cuda", dtype))
+    assert probs is None and got.shape == (B, L, 128)
+    valid = m.bool()
+    g, w = got.float().cpu()[valid].numpy(), want[valid].numpy()
+    if dtype == torch.float32:
+        assert np.abs(g - w).max() / np.abs(w).max() < util.FP32_REL_TOL
+    else:
+        # Q/K/V are rounded to bf16 after the projection in the fused path only; allow for it on top of the kernel tolerance
+        assert np.abs(g - w).max() < 2 * util.BF16_ABS_TOL
+    assert torch.count_nonzero(got.float().cpu()[~valid]).item() == 0
+
+
+def test_whole_model_matches_eager_fp32():
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DebertaV2Model
+    from turbodeberta_b200.model import FlashDebertaV2Model, patch_model
+    torch.manual_seed(5)
+    cfg = _cfg()
+    hf = DebertaV2Model(cfg).eval()
+    fl = FlashDebertaV2Model(cfg).eval()
+    fl.load_state_dict(hf.state_dict())
+    ids = torch.randint(0, 500, (3, 160))
+    mask = torch.ones(3, 160, dtype=torch.long)
+    mask[1, 100:] = 0
+    mask[2, 33:] = 0
+    with torch.no_grad():
+        want = hf(input_ids=ids, attention_mask=mask).last_hidden_state
+        got = fl.cuda()(input_ids=ids.cuda(), attention_mask=mask.cuda()).last_hidden_state.cpu()
+        got2 = fl(input_ids=ids.cuda(), attention_mask=mask.cuda()).last_hidden_state.cpu()      # cached tables
+    v = mask.bool()
+    assert (got[v] - want[v]).abs().max().item() / want[v].abs().max().item() < 2e-4
+    assert torch.equal(got, got2)
+    patched = patch_model(DebertaV2Model(cfg).eval())
+    patched.load_state_dict(hf.state_dict())
+    with torch.no_grad():
+        got3 = patched.cuda()(input_ids=ids.cuda(), attention_mask=mask.cuda()).last_hidden_state.cpu()
+    assert (got3[v] - want[v]).abs().max().item() / want[v].abs().max().item() < 2e-4
+
+
+def test_tables_follow_weight_updates():
+    """The cached relative tables must be rebuilt when a projection weight changes in place."""
+    from turbodeberta_b200.model import FlashDebertaV2Model
+    torch.manual_seed(6)
+    fl = FlashDebertaV2Model(_cfg()).eval().cuda()
+    ids = torch.randint(0, 500, (1, 64)).cuda()
+    with torch.no_grad():
+        a = fl(input_ids=ids).last_hidden_state.clone()
+        fl.encoder.layer[0].attention.self.key_proj.weight.mul_(1.5)
+        b = fl(input_ids=ids).last_hidden_state
+    assert not torch.equal(a, b)

@@ -15,6 +15,7 @@ which the reference kernel does not have.  Forward only, like the reference (``o
 """
 from __future__ import annotations
 
+import collections
 import math
 
 import torch
@@ -64,6 +65,24 @@ def _tables_from_args(q_pos, k_pos, q, position_buckets, max_relative_distance, 
     qr_exp = _relpos.expand(qr, idx, exp_dm) if (want_exp and qr is not None) else None
     return _relpos.RelPosTables(position_buckets, max_relative_distance, two_span, idx, sat + 1, kr, qr, kr_exp,
                                 qr_exp, exp_dm, (2 * exp_dm + 1 + 7) // 8 * 8)
+
+
+# Status words of calls made with check_status=False (no host sync at call time); read by check_pending_status().
+_PENDING_STATUS: collections.deque = collections.deque(maxlen=512)
+
+
+def check_pending_status() -> None:
+    """Read (one synchronisation) the device status words of every call since the last check that was made
+    with ``check_status=False`` and raise if any bounded device wait gave up or any ``cu_seqlens`` was malformed."""
+    if not _PENDING_STATUS:
+        return
+    pending = list(_PENDING_STATUS)
+    _PENDING_STATUS.clear()
+    by_dev = {}
+    for st in pending:
+        by_dev.setdefault(st.device, []).append(st)
+    for dev, sts in by_dev.items():
+        _check_status(torch.stack(sts).amax(dim=0))
 
 
 def _check_status(status: torch.Tensor):
@@ -118,6 +137,8 @@ class _FixedFn(torch.autograd.Function):
         cabi.check(rc)
         if check:
             _check_status(status)
+        else:
+            _PENDING_STATUS.append(status)
         ctx.mark_non_differentiable(o)
         return (o, lse, status) if return_lse else (o, None, status)
 

@@ -18,7 +18,7 @@ import math
 import torch
 
 from .. import _cabi as cabi
-from .flash_attention import _check_status, _tables_from_args
+from .flash_attention import _PENDING_STATUS, _check_status, _tables_from_args
 
 
 class _VarlenFn(torch.autograd.Function):
@@ -63,6 +63,8 @@ class _VarlenFn(torch.autograd.Function):
         cabi.check(rc)
         if check:
             _check_status(status)
+        else:
+            _PENDING_STATUS.append(status)
         ctx.mark_non_differentiable(o)
         return (o, lse, status) if return_lse else (o, None, status)
 
