@@ -2,25 +2,29 @@
 //
 // One CTA = one (sequence, head, 128-query tile); it walks the sequence's keys in tiles of 128:
 //
-//   S  = Q . K^T                         128x128   UMMA  (A = Q tile, B = K tile, both K-major in smem)
-//   C  = Q . KrX[win]^T                  128x256   UMMA  content->position band
-//   P2 = K . QrX[win]^T                  128x256   UMMA  position->content band (rows = keys)
+//   S  = Q . K^T                         128x128      UMMA  (A = Q tile, B = K tile, both K-major in smem)
+//   C  = Q . KrX[win]^T                  2 x 128x128  UMMA  content->position band, as two column halves
+//   P2 = K . QrX[win]^T                  2 x 128x128  UMMA  position->content band (rows = keys), two halves
 //   s[i][j] = (S[i][j] + C[i][i-j+127] + P2[j][i-j+127]) * scale ;  mask ;  online softmax
-//   O += P . V                           128x64    UMMA  (A = P as bf16 in tensor memory, B = V tile, MN-major)
+//   O += P . V                           128x64       UMMA  (A = P as bf16 in tensor memory, B = V tile, MN-major)
 //
 // KrX / QrX are the distance-expanded tables (row x <-> distance x - exp_delta_max), so the rows a tile
 // needs are the contiguous window win = [q0 - k0 - 127 + exp_delta_max, +256), one TMA box.  The diagonal
 // read C[i][i-j+127] cannot be done from registers (the column depends on the lane), so both bands are
-// drained from tensor memory to shared memory as bf16 rows and read back skewed: the c2p row belongs to
-// the reading thread; the p2c rows are written by the thread that owns the key and read by every query.
+// drained from tensor memory to shared memory as bf16 rows and read back skewed.
 //
-// Warp roles (192 threads): warps 0-3 = drain + softmax + epilogue (thread t owns query row t and
-// tensor-memory lane t), warp 4 = TMA producer (one lane), warp 5 = tensor-memory allocation + MMA issue
-// (one lane).  All hand-offs are mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort
-// flag and the status word, after which every role keeps walking its loop without waiting so that the
-// CTA-wide barriers still match, tensor memory is freed, and the host reports TDB_ERR_TIMEOUT.
+// Warp roles (576 threads): warps 0-15 do the CUDA-core work; warp w owns tensor-memory lanes 32*(w%4)..+31
+// (query rows, or key rows of P2) and column group w/4, i.e. four threads share a query row and each handles 32
+// of the 128 keys, which puts four warps on every scheduler to hide latency.  Warp 16 = TMA producer (lane 0:
+// tables and K; lane 1: Q and V), warp 17 = tensor-memory allocation + MMA issue (one lane).
 //
-// Tensor-memory columns: [0,128) S (P overlays [0,64) once S is in registers), [128,192) O, [256,512) band.
+// Pipeline: the band halves go through a two-slot ring in tensor memory, so the MMA of one half overlaps the
+// drain of the other, and the bands and S of key tile t+1 are issued while the CUDA warps run the softmax of
+// tile t.  All hand-offs are mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort flag and
+// the status word, after which every role keeps walking its loop without waiting so that the CTA-wide barriers
+// still match, tensor memory is freed, and the host reports TDB_ERR_TIMEOUT.
+//
+// Tensor-memory columns: [0,128) S, [128,192) O, [192,320) ring slot A, [320,448) ring slot B, [448,512) P (bf16).
 #include "tdb_internal.h"
 #include "ptx_sm100.cuh"
 #include <cudaTypedefs.h>
@@ -32,23 +36,46 @@ using namespace ptx;
 
 namespace {
 
-constexpr int BQ = 128, BK = 128, HD = 64, BAND = 256;
-constexpr int NTHREADS = 192;
+constexpr int BQ = 128, BK = 128, HD = 64, BAND = 256, HALF = 128;
+constexpr int GROUPS = 4;                       // threads per query row
+constexpr int KPT = BK / GROUPS;                // keys per thread in the softmax (32)
+constexpr int NCW = 4 * GROUPS;                 // CUDA-core warps
+constexpr int NCT = NCW * 32;                   // CUDA-core threads
+constexpr int NTHREADS = (NCW + 2) * 32;
 constexpr int STG_STRIDE = 336;                 // bytes per staging row: 160 bf16 + 16 pad (odd multiple of 16)
 constexpr int STG_COLS = 160;
 constexpr uint32_t OFF_Q = 0, OFF_K = 16384, OFF_V = 32768, OFF_KR = 49152, OFF_QR = 81920;
-constexpr uint32_t OFF_STC = 114688, OFF_STP = OFF_STC + BQ * STG_STRIDE, OFF_BAR = OFF_STP + BK * STG_STRIDE;
+constexpr uint32_t OFF_STC = 114688, OFF_STP = OFF_STC + BQ * STG_STRIDE, OFF_XCH = OFF_STP + BK * STG_STRIDE;
+constexpr uint32_t OFF_BAR = OFF_XCH + GROUPS * BQ * 4;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;   // + slack for the 1024-byte alignment of the base
-static_assert(OFF_STP % 16 == 0 && OFF_BAR % 16 == 0, "staging offsets must stay 16-byte aligned");
+static_assert(OFF_STP % 16 == 0 && OFF_XCH % 16 == 0 && OFF_BAR % 16 == 0, "offsets must stay 16-byte aligned");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
-constexpr uint32_t TM_S = 0, TM_O = 128, TM_BAND = 256, TM_COLS = 512;
+constexpr uint32_t TM_S = 0, TM_O = 128, TM_RING = 192, TM_P = 448, TM_COLS = 512;
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per wait, then give up
 
 enum Bar { Q_FULL = 0, K_FULL, K_EMPTY, V_FULL, V_EMPTY, KR_FULL, KR_EMPTY, QR_FULL, QR_EMPTY,
-           SC_FULL, BAND_FREE, P2_FULL, P_READY, O_FULL, DONE, NBARS };
+           S_FULL, S_TAKEN, RING_FULL_A, RING_FULL_B, RING_FREE_A, RING_FREE_B, P_READY, O_FULL, DONE, NBARS };
+static_assert(NBARS * 8 <= 160, "barrier block");
 
 struct TileListHeader { int32_t n_tiles; int32_t pad[3]; };
+
+// Optional event trace of one CTA (build with -DTDB_TIMELINE=<blockIdx.x>): (event, SM clock) pairs per role.
+#ifdef TDB_TIMELINE
+constexpr int TL_MAX = 256;
+__device__ long long g_timeline[3][TL_MAX][2];
+__device__ int g_timeline_n[3];
+#define TDB_TL(role, evt)                                                                     \
+  do {                                                                                        \
+    if (blockIdx.x == (TDB_TIMELINE) && blockIdx.y == 0 && tl_n[role] < TL_MAX) {             \
+      g_timeline[role][tl_n[role]][0] = (evt);                                                \
+      g_timeline[role][tl_n[role]][1] = clock64();                                            \
+      g_timeline_n[role] = ++tl_n[role];                                                      \
+    }                                                                                         \
+  } while (0)
+#else
+#define TDB_TL(role, evt) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Packed form: list of (sequence, first query row) per 128-row tile, built on the device from
@@ -91,33 +118,37 @@ __global__ void __launch_bounds__(1024) build_tile_list_kernel(const int32_t* __
   }
 }
 
-__device__ __forceinline__ float bf16_bits_to_float(uint32_t u16) { return __uint_as_float(u16 << 16); }
-
 __device__ __forceinline__ float lds_bf16(uint32_t addr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return bf16_bits_to_float((uint32_t)v);
+  return __uint_as_float(((uint32_t)v) << 16);
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 __device__ __forceinline__ void sts_128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-__device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void bar_all_cuda_warps() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
+__device__ __forceinline__ void bar_quadrant(int qd) { asm volatile("bar.sync %0, %1;" ::"r"(2 + qd), "n"(GROUPS * 32) : "memory"); }
 
-// Move STG_COLS fp32 columns of this thread's tensor-memory lane, starting at `taddr`, to one bf16 staging row.
-__device__ __forceinline__ void drain_band_row(uint32_t taddr, uint32_t row_saddr) {
+// Move 32 fp32 columns of this thread's tensor-memory lane to 32 bf16 of a staging row.
+__device__ __forceinline__ void drain_chunk(uint32_t taddr, uint32_t dst_saddr) {
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+  tmem_ld_wait32(r);
 #pragma unroll
-  for (int c = 0; c < STG_COLS / 32; ++c) {
-    uint32_t r[32];
-    tmem_ld32(taddr + c * 32, r);
-    tmem_ld_wait32(r);
+  for (int g = 0; g < 4; ++g) {
+    uint32_t w[4];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        w[e] = pack_bf16x2(__uint_as_float(r[g * 8 + 2 * e]), __uint_as_float(r[g * 8 + 2 * e + 1]));
-      sts_128(row_saddr + c * 64 + g * 16, w[0], w[1], w[2], w[3]);
-    }
+    for (int e = 0; e < 4; ++e)
+      w[e] = pack_bf16x2(__uint_as_float(r[g * 8 + 2 * e]), __uint_as_float(r[g * 8 + 2 * e + 1]));
+    sts_128(dst_saddr + g * 16, w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -164,29 +195,35 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     if (s_skip) return;
   }
   const int n_kv = (len + BK - 1) / BK;
+#ifdef TDB_TIMELINE
+  int tl_n[3] = {0, 0, 0};
+#endif
 
   // ---- shared memory carve-up ----------------------------------------------------------------
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t sQ = sbase + OFF_Q, sK = sbase + OFF_K, sV = sbase + OFF_V, sKr = sbase + OFF_KR, sQr = sbase + OFF_QR;
-  const uint32_t stC = sbase + OFF_STC, stP = sbase + OFF_STP;
+  const uint32_t stC = sbase + OFF_STC, stP = sbase + OFF_STP, sX = sbase + OFF_XCH;
   const uint32_t bars = sbase + OFF_BAR;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_BAR + 128);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_BAR + 136);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_BAR + 160);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_BAR + 168);
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
   auto wait = [&](int i, uint32_t parity) { return mbar_wait(bar(i), parity, abort_flag, p.status, 1 + i, WAIT_LIMIT_NS); };
 
   if (tid == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < NBARS; ++i) mbar_init(bar(i), (i == BAND_FREE || i == P_READY) ? 128u : 1u);
+    for (int i = 0; i < NBARS; ++i) {
+      const bool by_warps = (i == S_TAKEN || i == RING_FREE_A || i == RING_FREE_B || i == P_READY);
+      mbar_init(bar(i), by_warps ? (uint32_t)NCW : 1u);
+    }
     fence_mbar_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == NCW && lane == 0) {
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
     if (C2P) prefetch_tmap(&tm_kr);
     if (P2C) prefetch_tmap(&tm_qr);
   }
-  if (warp == 5) {
+  if (warp == NCW + 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TM_COLS);
     tmem_relinquish();
   }
@@ -195,11 +232,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 4) {
-    // ================================ TMA producer ==========================================
-    if (lane == 0) {
-      mbar_expect_tx(bar(Q_FULL), BQ * HD * 2);
-      tma_load_4d(sQ, &tm_q, bar(Q_FULL), 0, (int)(tok0 + q0), h, bcoord);
+  if (warp == NCW) {
+    // ================================ TMA producers ==========================================
+    if (lane == 0) {                       // relative tables and K
       for (int it = 0; it < n_kv; ++it) {
         const int k0 = it * BK;
         const uint32_t pe = (uint32_t)((it - 1) & 1);
@@ -211,195 +246,276 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             mbar_expect_tx(bar(KR_FULL), BAND * HD * 2);
             tma_load_3d(sKr, &tm_kr, bar(KR_FULL), 0, x0, h);
           }
+          TDB_TL(2, 100 + it);
         }
         if (it > 0) wait(K_EMPTY, pe);
         if (!*abort_flag) {
           mbar_expect_tx(bar(K_FULL), BK * HD * 2);
           tma_load_4d(sK, &tm_k, bar(K_FULL), 0, (int)(tok0 + k0), h, bcoord);
         }
+        TDB_TL(2, 200 + it);
         if (P2C) {
           if (it > 0) wait(QR_EMPTY, pe);
           if (!*abort_flag) {
             mbar_expect_tx(bar(QR_FULL), BAND * HD * 2);
             tma_load_3d(sQr, &tm_qr, bar(QR_FULL), 0, x0, h);
           }
+          TDB_TL(2, 300 + it);
         }
-        if (it > 0) wait(V_EMPTY, pe);
+      }
+    } else if (lane == 1) {                // Q once, then V
+      mbar_expect_tx(bar(Q_FULL), BQ * HD * 2);
+      tma_load_4d(sQ, &tm_q, bar(Q_FULL), 0, (int)(tok0 + q0), h, bcoord);
+      for (int it = 0; it < n_kv; ++it) {
+        if (it > 0) wait(V_EMPTY, (uint32_t)((it - 1) & 1));
         if (!*abort_flag) {
           mbar_expect_tx(bar(V_FULL), BK * HD * 2);
-          tma_load_4d(sV, &tm_v, bar(V_FULL), 0, (int)(tok0 + k0), h, bcoord);
+          tma_load_4d(sV, &tm_v, bar(V_FULL), 0, (int)(tok0 + it * BK), h, bcoord);
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == NCW + 1) {
     // ================================ MMA issuer ============================================
     if (lane == 0) {
       constexpr uint32_t ID_S = make_idesc_bf16(128, BK, 0);
-      constexpr uint32_t ID_BAND = make_idesc_bf16(128, BAND, 0);
+      constexpr uint32_t ID_HALF = make_idesc_bf16(128, HALF, 0);
       constexpr uint32_t ID_PV = make_idesc_bf16(128, HD, 1);
+      constexpr uint64_t HALF_ROWS = (uint64_t)((HALF * HD * 2) >> 4);      // descriptor offset of the upper 128 table rows
       const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
       const uint64_t dKr = smem_desc_sw128(sKr), dQr = smem_desc_sw128(sQr);
-      const uint32_t tS = tmem + TM_S, tO = tmem + TM_O, tB = tmem + TM_BAND;
-      int band_n = 0;
-      wait(Q_FULL, 0);
-      for (int it = 0; it < n_kv; ++it) {
-        const uint32_t ph = (uint32_t)(it & 1);
-        wait(K_FULL, ph);
+      const uint32_t tS = tmem + TM_S, tO = tmem + TM_O, tP = tmem + TM_P;
+      const uint32_t tRing[2] = {tmem + TM_RING, tmem + TM_RING + HALF};
+      int fills[2] = {0, 0};               // how often each ring slot has been filled so far
+
+      // One band half: A (128 rows) x table rows [128*half, +128) -> ring slot `half`.
+      auto band_half = [&](uint64_t dA, uint64_t dTab, int half) {
+        if (fills[half] > 0) wait(half ? RING_FREE_B : RING_FREE_A, (uint32_t)((fills[half] - 1) & 1));
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tRing[half], dA + 2 * k, dTab + (uint64_t)half * HALF_ROWS + 2 * k, ID_HALF, k > 0);
+        tc_commit(bar(half ? RING_FULL_B : RING_FULL_A));
+        ++fills[half];
+      };
+      auto issue_c = [&](int t) {          // content->position band of key tile t
+        wait(KR_FULL, (uint32_t)(t & 1));
+        TDB_TL(1, 1000 + t);
+        band_half(dQ, dKr, 0);
+        TDB_TL(1, 1100 + t);
+        band_half(dQ, dKr, 1);
+        tc_commit(bar(KR_EMPTY));
+        TDB_TL(1, 1200 + t);
+      };
+      auto issue_s = [&](int t) {          // content score of key tile t
+        wait(K_FULL, (uint32_t)(t & 1));
+        if (t > 0) wait(S_TAKEN, (uint32_t)((t - 1) & 1));
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQ + 2 * k, dK + 2 * k, ID_S, k > 0);
-        if (C2P) {
-          wait(KR_FULL, ph);
-          if (band_n > 0) wait(BAND_FREE, (uint32_t)((band_n - 1) & 1));
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss(tB, dQ + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
-          ++band_n;
-        }
-        tc_commit(bar(SC_FULL));
-        if (C2P) tc_commit(bar(KR_EMPTY));
+        tc_commit(bar(S_FULL));
+        TDB_TL(1, 2000 + t);
+      };
+      auto issue_p2 = [&](int t) {         // position->content band of key tile t; releases K afterwards
         if (P2C) {
-          wait(QR_FULL, ph);
-          if (band_n > 0) wait(BAND_FREE, (uint32_t)((band_n - 1) & 1));
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss(tB, dK + 2 * k, dQr + 2 * k, ID_BAND, k > 0);
-          ++band_n;
-          tc_commit(bar(P2_FULL));
+          wait(QR_FULL, (uint32_t)(t & 1));
+          TDB_TL(1, 3000 + t);
+          band_half(dK, dQr, 0);
+          TDB_TL(1, 3100 + t);
+          band_half(dK, dQr, 1);
           tc_commit(bar(QR_EMPTY));
         }
         tc_commit(bar(K_EMPTY));
+        TDB_TL(1, 3200 + t);
+      };
+
+      TDB_TL(1, 1);
+      wait(Q_FULL, 0);
+      TDB_TL(1, 2);
+      if (C2P) issue_c(0);
+      issue_s(0);
+      issue_p2(0);
+      for (int it = 0; it < n_kv; ++it) {
+        const uint32_t ph = (uint32_t)(it & 1);
+        const bool nxt = it + 1 < n_kv;
+        if (nxt) {
+          if (C2P) issue_c(it + 1);
+          issue_s(it + 1);
+        }
         wait(V_FULL, ph);
+        TDB_TL(1, 4000 + it);
         wait(P_READY, ph);
+        TDB_TL(1, 4100 + it);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
-          mma_ts(tO, tS + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (it > 0 || k > 0) ? 1u : 0u);
+          mma_ts(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (it > 0 || k > 0) ? 1u : 0u);
         tc_commit(bar(O_FULL));
         tc_commit(bar(V_EMPTY));
+        TDB_TL(1, 4200 + it);
+        if (nxt) issue_p2(it + 1);
       }
       // Everything issued above must have retired before tensor memory is released.
       tc_commit(bar(DONE));
       int never = 0;                       // this wait runs even after an abort, with its own limit
       mbar_wait(bar(DONE), 0, &never, p.status, 1 + DONE, WAIT_LIMIT_NS);
+      TDB_TL(1, 9);
     }
   } else {
     // ================================ drain + softmax + epilogue ============================
-    const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
-    const uint32_t tS = tmem + lane_base + TM_S, tO = tmem + lane_base + TM_O, tB = tmem + lane_base + TM_BAND;
+    const int qd = warp & 3, grp = warp >> 2;
+    const int row_t = qd * 32 + lane;                                  // tensor-memory lane = query row (or key row of P2)
+    const uint32_t lane_base = ((uint32_t)(qd * 32)) << 16;
+    const uint32_t tS = tmem + lane_base + TM_S + KPT * grp;
+    const uint32_t tO = tmem + lane_base + TM_O + (HD / GROUPS) * grp;
+    const uint32_t tP = tmem + lane_base + TM_P + (KPT / 2) * grp;
+    const uint32_t tRingMine = tmem + lane_base + TM_RING + 32 * grp;  // + HALF for slot B
     const float sl2 = p.sm_scale * 1.4426950408889634f;
-    const uint32_t c_row = stC + (uint32_t)tid * STG_STRIDE;          // this thread's c2p staging row
-    const uint32_t p_row = stP + (uint32_t)tid * STG_STRIDE;          // the p2c staging row of key `tid`
-    const uint32_t c_read = c_row + 2u * (uint32_t)lane + 2u * (BK - 1);   // element for j is at c_read - 2*j
-    const uint32_t p_read = stP + 2u * (uint32_t)tid + 62u;           // element for j is at p_read + j*STRIDE - 2*(j%32)
-    float m_run = -CUDART_INF_F, l_run = 0.f;
+    // staging rows: c2p row i holds band columns [32*qd, +160); p2c row j holds band columns [96 - 32*(j/32), +160)
+    const uint32_t c_row = stC + (uint32_t)row_t * STG_STRIDE;
+    const uint32_t p_row = stP + (uint32_t)row_t * STG_STRIDE;
+    const uint32_t c_read = c_row + 2u * (uint32_t)(lane + (BK - 1) - KPT * grp);          // key e of this thread: c_read - 2e
+    const uint32_t p_read = stP + (uint32_t)(KPT * grp) * STG_STRIDE + 2u * (uint32_t)(row_t + 31);  // + e*STRIDE - 2e
+    const uint32_t x_mine = sX + 4u * (uint32_t)(grp * BQ + row_t);
+    float m_run = -CUDART_INF_F, l_part = 0.f;
+    int drains[2] = {0, 0};
+
+    // Drain one band half from ring slot `half`.  kind 0: c2p (window starts at 32*qd), kind 1: p2c (96 - 32*qd).
+    auto drain_half = [&](int half, int kind) {
+      wait(half ? RING_FULL_B : RING_FULL_A, (uint32_t)(drains[half] & 1));
+      ++drains[half];
+      tc_fence_after();
+      const int col = HALF * half + 32 * grp;                          // band column of this thread's chunk
+      const int local = col - (kind == 0 ? 32 * qd : 96 - 32 * qd);    // position inside the staging row
+      if (local >= 0 && local + 32 <= STG_COLS)
+        drain_chunk(tRingMine + (uint32_t)(HALF * half), (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(half ? RING_FREE_B : RING_FREE_A));
+    };
+    auto drain_tile = [&]() {
+      if (C2P) { drain_half(0, 0); drain_half(1, 0); }
+      if (P2C) { drain_half(0, 1); drain_half(1, 1); }
+    };
+
+#define TL0(evt) do { if (tid == 0) TDB_TL(0, evt); } while (0)
+    TL0(1);
+    drain_tile();                                                      // bands of key tile 0
+    TL0(2);
+    bar_all_cuda_warps();
+    TL0(3);
 
     for (int it = 0; it < n_kv; ++it) {
       const uint32_t ph = (uint32_t)(it & 1);
-      const int nvalid = len - it * BK;                               // >= 1; keys j >= nvalid are masked
-      wait(SC_FULL, ph);
+      const int nvalid = len - it * BK - KPT * grp;                    // keys e >= nvalid of this thread are masked
+      TL0(10000 + it);
+      wait(S_FULL, ph);
+      TL0(11000 + it);
       tc_fence_after();
-      if (C2P) {
-        drain_band_row(tB + (uint32_t)(warp * 32), c_row);             // columns [32w, 32w+160)
-        tc_fence_before();
-        mbar_arrive(bar(BAND_FREE));
-      }
-      if (P2C) {
-        wait(P2_FULL, ph);
-        tc_fence_after();
-        named_bar_sync_128();                                          // readers of the previous tile are done
-        drain_band_row(tB + (uint32_t)(96 - warp * 32), p_row);        // columns [96-32w, 256-32w)
-        tc_fence_before();
-        mbar_arrive(bar(BAND_FREE));
-        named_bar_sync_128();                                          // all key rows are visible
-      }
-      float s[BK];
+      float s[KPT];
       {
         uint32_t* sr = reinterpret_cast<uint32_t*>(s);
-        tmem_ld32(tS + 0, sr + 0); tmem_ld32(tS + 32, sr + 32); tmem_ld32(tS + 64, sr + 64); tmem_ld32(tS + 96, sr + 96);
-        tmem_ld_wait32(sr + 0); tmem_ld_wait32(sr + 32); tmem_ld_wait32(sr + 64); tmem_ld_wait32(sr + 96);
+        tmem_ld32(tS, sr);
+        tmem_ld_wait32(sr);
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(S_TAKEN));
       float mx = -CUDART_INF_F;
-      if (nvalid >= BK) {
+      if (nvalid >= KPT) {
 #pragma unroll
-        for (int j = 0; j < BK; ++j) {
-          float x = s[j];
-          if (C2P) x += lds_bf16(c_read - 2u * j);
-          if (P2C) x += lds_bf16(p_read + (uint32_t)(j * STG_STRIDE - 2 * (j & 31)));
+        for (int e = 0; e < KPT; ++e) {
+          float x = s[e];
+          if (C2P) x += lds_bf16(c_read - 2u * e);
+          if (P2C) x += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
           x *= sl2;
-          s[j] = x;
+          s[e] = x;
           mx = fmaxf(mx, x);
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < BK; ++j) {
-          float x = s[j];
-          if (C2P) x += lds_bf16(c_read - 2u * j);
-          if (P2C) x += lds_bf16(p_read + (uint32_t)(j * STG_STRIDE - 2 * (j & 31)));
-          x = (j < nvalid) ? x * sl2 : -CUDART_INF_F;
-          s[j] = x;
+        for (int e = 0; e < KPT; ++e) {
+          float x = s[e];
+          if (C2P) x += lds_bf16(c_read - 2u * e);
+          if (P2C) x += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
+          x = (e < nvalid) ? x * sl2 : -CUDART_INF_F;
+          s[e] = x;
           mx = fmaxf(mx, x);
         }
       }
+      // row maximum over the four threads of the row
+      TL0(12000 + it);
+      sts_f32(x_mine, mx);
+      bar_quadrant(qd);
+      TL0(13000 + it);
+#pragma unroll
+      for (int g = 0; g < GROUPS; ++g) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(g * BQ + row_t)));
       const float m_new = fmaxf(m_run, mx);
       const float alpha = ex2(m_run - m_new);
       if (it > 0) {
         wait(O_FULL, (uint32_t)((it - 1) & 1));
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          uint32_t r[16];
+          tmem_ld16(tO, r);
+          tmem_ld_wait16(r);
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO + c * 32, r);
-            tmem_ld_wait32(r);
-#pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-            tmem_st32(tO + c * 32, r);
-          }
+          for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+          tmem_st16(tO, r);
         }
       }
+      TL0(14000 + it);
       float lsum = 0.f;
-      uint32_t pk[BK / 2];
+      uint32_t pk[KPT / 2];
 #pragma unroll
-      for (int j = 0; j < BK; j += 2) {
-        float a = ex2(s[j] - m_new), b = ex2(s[j + 1] - m_new);
+      for (int e = 0; e < KPT; e += 2) {
+        float a = ex2(s[e] - m_new), b = ex2(s[e + 1] - m_new);
         lsum += a + b;
-        pk[j / 2] = pack_bf16x2(a, b);
+        pk[e / 2] = pack_bf16x2(a, b);
       }
-      l_run = l_run * alpha + lsum;
+      l_part = l_part * alpha + lsum;
       m_run = m_new;
-      tmem_st32(tS + 0, pk);
-      tmem_st32(tS + 32, pk + 32);
+      tmem_st16(tP, pk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar(P_READY));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_READY));
+      TL0(15000 + it);
+      bar_all_cuda_warps();                                            // staging rows and the exchange buffer are free again
+      TL0(16000 + it);
+      if (it + 1 < n_kv) drain_tile();
+      TL0(17000 + it);
+      bar_all_cuda_warps();                                            // staging of the next tile is complete
+      TL0(18000 + it);
     }
     // ---- epilogue: O / l -> global ----
+    sts_f32(x_mine, l_part);
+    bar_quadrant(qd);
+    float l_tot = 0.f;
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) l_tot += lds_f32(sX + 4u * (uint32_t)(g * BQ + row_t));
     wait(O_FULL, (uint32_t)((n_kv - 1) & 1));
+    TL0(20000);
     tc_fence_after();
-    const int row = q0 + tid;
-    const float inv = 1.f / l_run;
-    uint32_t outw[HD / 2];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tO + c * 32, r);
-      tmem_ld_wait32(r);
-#pragma unroll
-      for (int e = 0; e < 32; e += 2)
-        outw[c * 16 + e / 2] = pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
-    }
+    const int row = q0 + row_t;
+    const float inv = 1.f / l_tot;
+    uint32_t r[16];
+    tmem_ld16(tO, r);
+    tmem_ld_wait16(r);
     tc_fence_before();
     if (row < rows) {
       const bool valid = row < len;
-      uint4* dst = reinterpret_cast<uint4*>(obase + (int64_t)tid * p.o_st);
+      uint32_t outw[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        dst[i] = valid ? make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]) : make_uint4(0, 0, 0, 0);
-      if (p.lse)
+      for (int e = 0; e < 16; e += 2)
+        outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
+      uint4* dst = reinterpret_cast<uint4*>(obase + (int64_t)row_t * p.o_st + (HD / GROUPS) * grp);
+      dst[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+      dst[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+      if (p.lse && grp == 0)
         p.lse[(int64_t)bcoord * p.lse_sb + (int64_t)h * p.lse_sh + tok0 + row] =
-            valid ? (m_run * 0.6931471805599453f + logf(l_run)) : 0.f;
+            valid ? (m_run * 0.6931471805599453f + logf(l_tot)) : 0.f;
     }
+    TL0(21000);
   }
 
   // ---- teardown ------------------------------------------------------------------------------
@@ -410,7 +526,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 5) tmem_dealloc(tmem, TM_COLS);
+  if (warp == NCW + 1) tmem_dealloc(tmem, TM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -496,6 +612,14 @@ int static_tile_scratch(void** ptr) {
   *ptr = addr[dev];
   return TDB_OK;
 }
+
+#ifdef TDB_TIMELINE
+extern "C" TDB_API int tdb_debug_timeline(long long* out, int* counts) {
+  if (cudaMemcpyFromSymbol(out, g_timeline, sizeof(long long) * 3 * TL_MAX * 2) != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(counts, g_timeline_n, sizeof(int) * 3) != cudaSuccess) return -1;
+  return TL_MAX;
+}
+#endif
 
 size_t umma_workspace_bytes(int n_seqs, int64_t total_tokens) {
   int64_t cap = (total_tokens + BQ - 1) / BQ + n_seqs + 1;

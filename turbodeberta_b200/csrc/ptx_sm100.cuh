@@ -144,6 +144,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       ::TDB_IN8(r, 0), TDB_IN8(r, 8), TDB_IN8(r, 16), TDB_IN8(r, 24), "r"(taddr)
       : "memory");
 }
+// 16-column variants (same lane mapping as the 32-column forms).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : TDB_OUT8(r, 0), TDB_OUT8(r, 8)
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : TDB_IO8(r, 0), TDB_IO8(r, 8) : : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::TDB_IN8(r, 0), TDB_IN8(r, 8), "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------ descriptors

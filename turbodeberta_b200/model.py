@@ -17,6 +17,7 @@ one fused kernel call.  Differences from the reference module, all on the host s
 from __future__ import annotations
 
 import math
+import weakref
 
 import torch
 from torch import nn
@@ -46,14 +47,16 @@ def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int) -
     """Reduce a ``[B,L]``, ``[B,L,L]`` or ``[B,1,L,L]`` mask to per-row key validity.
 
     Costs one device synchronisation (two booleans are read back); the result is cached on the mask
-    tensor's identity and version, so the 24 layers of one forward share it.  A mask that is not the
+    tensor object (weak reference) and its version, so the 24 layers of one forward share it.  A mask that is not the
     outer product of a token-validity vector (i.e. whose valid queries disagree about the keys) is rejected."""
     if attention_mask is None:
         return MaskInfo(True, True, None, None)
-    key = (attention_mask.data_ptr(), tuple(attention_mask.shape), attention_mask._version, attention_mask.dtype)
+    key = id(attention_mask)
     hit = _MASK_CACHE.get(key)
     if hit is not None:
-        return hit
+        ref, version, cached = hit
+        if ref() is attention_mask and version == attention_mask._version:     # same live tensor object, unmodified
+            return cached
     m = attention_mask
     if m.dim() == 4:
         if m.shape[1] != 1:
@@ -80,7 +83,7 @@ def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int) -
     info = MaskInfo(bool(flags[0]), bool(flags[1]), seqlens, key_mask)
     if len(_MASK_CACHE) > 8:
         _MASK_CACHE.clear()
-    _MASK_CACHE[key] = info
+    _MASK_CACHE[key] = (weakref.ref(attention_mask), attention_mask._version, info)
     return info
 
 
