@@ -279,6 +279,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     if (lane == 0) {
       constexpr uint32_t ID_S = make_idesc_bf16(128, BK, 0);
       constexpr uint32_t ID_HALF = make_idesc_bf16(128, HALF, 0);
+      constexpr uint32_t ID_BAND = make_idesc_bf16(128, BAND, 0);
       constexpr uint32_t ID_PV = make_idesc_bf16(128, HD, 1);
       constexpr uint64_t HALF_ROWS = (uint64_t)((HALF * HD * 2) >> 4);      // descriptor offset of the upper 128 table rows
       const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
@@ -297,13 +298,18 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_commit(bar(half ? RING_FULL_B : RING_FULL_A));
         ++fills[half];
       };
-      auto issue_c = [&](int t) {          // content->position band of key tile t
+      auto issue_c = [&](int t) {          // content->position band of key tile t: one 256-column product into both slots
         wait(KR_FULL, (uint32_t)(t & 1));
         TDB_TL(1, 1000 + t);
-        band_half(dQ, dKr, 0);
-        TDB_TL(1, 1100 + t);
-        band_half(dQ, dKr, 1);
+        if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
+        if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQ + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
+        tc_commit(bar(RING_FULL_A));
+        tc_commit(bar(RING_FULL_B));
         tc_commit(bar(KR_EMPTY));
+        ++fills[0]; ++fills[1];
         TDB_TL(1, 1200 + t);
       };
       auto issue_s = [&](int t) {          // content score of key tile t
@@ -336,10 +342,10 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       issue_p2(0);
       for (int it = 0; it < n_kv; ++it) {
         const uint32_t ph = (uint32_t)(it & 1);
-        const bool nxt = it + 1 < n_kv;
-        if (nxt) {
-          if (C2P) issue_c(it + 1);
+        if (it + 1 < n_kv) {
+          if (C2P) issue_c(it + 1);        // runs while the CUDA warps are in the softmax of tile `it`
           issue_s(it + 1);
+          issue_p2(it + 1);                // each half starts as soon as its ring slot has been drained of C
         }
         wait(V_FULL, ph);
         TDB_TL(1, 4000 + it);
@@ -352,7 +358,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_commit(bar(O_FULL));
         tc_commit(bar(V_EMPTY));
         TDB_TL(1, 4200 + it);
-        if (nxt) issue_p2(it + 1);
       }
       // Everything issued above must have retired before tensor memory is released.
       tc_commit(bar(DONE));
@@ -392,14 +397,13 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(half ? RING_FREE_B : RING_FREE_A));
     };
-    auto drain_tile = [&]() {
-      if (C2P) { drain_half(0, 0); drain_half(1, 0); }
-      if (P2C) { drain_half(0, 1); drain_half(1, 1); }
-    };
+    auto drain_c = [&]() { if (C2P) { drain_half(0, 0); drain_half(1, 0); } };
+    auto drain_p2 = [&]() { if (P2C) { drain_half(0, 1); drain_half(1, 1); } };
 
 #define TL0(evt) do { if (tid == 0) TDB_TL(0, evt); } while (0)
     TL0(1);
-    drain_tile();                                                      // bands of key tile 0
+    drain_c();                                                         // bands of key tile 0
+    drain_p2();
     TL0(2);
     bar_all_cuda_warps();
     TL0(3);
@@ -420,26 +424,51 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(S_TAKEN));
-      float mx = -CUDART_INF_F;
+      // Phase 1: add the content->position term, then hand the c2p staging rows (shared only inside the
+      // quadrant) to the next key tile at once, so that its position->content products can run during phase 2.
+      if (C2P) {
+#pragma unroll
+        for (int e = 0; e < KPT; ++e) s[e] += lds_bf16(c_read - 2u * e);
+        TL0(11500 + it);
+        bar_quadrant(qd);
+        if (it + 1 < n_kv) drain_c();
+        TL0(11800 + it);
+      }
+      // Phase 2.  Scores stay unscaled in s[]; the exponentials are taken at once against the reference exponent of the
+      // previous tiles (0 on the first tile) so that the MUFU work overlaps the shared-memory reads, and are
+      // redone only for rows whose new maximum is more than 2^8 above (or, on the first tile, 2^64 below) it.
+      const float m_prev = (it > 0) ? m_run : 0.f;
+      float mx = -CUDART_INF_F, lsum = 0.f;
+      uint32_t pk[KPT / 2];
       if (nvalid >= KPT) {
 #pragma unroll
-        for (int e = 0; e < KPT; ++e) {
-          float x = s[e];
-          if (C2P) x += lds_bf16(c_read - 2u * e);
-          if (P2C) x += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
-          x *= sl2;
-          s[e] = x;
-          mx = fmaxf(mx, x);
+        for (int e = 0; e < KPT; e += 2) {
+          float x0 = s[e], x1 = s[e + 1];
+          if (P2C) {
+            x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
+            x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
+          }
+          s[e] = x0; s[e + 1] = x1;
+          mx = fmaxf(mx, fmaxf(x0, x1));
+          const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
+          lsum += a + b;
+          pk[e / 2] = pack_bf16x2(a, b);
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < KPT; ++e) {
-          float x = s[e];
-          if (C2P) x += lds_bf16(c_read - 2u * e);
-          if (P2C) x += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
-          x = (e < nvalid) ? x * sl2 : -CUDART_INF_F;
-          s[e] = x;
-          mx = fmaxf(mx, x);
+        for (int e = 0; e < KPT; e += 2) {
+          float x0 = s[e], x1 = s[e + 1];
+          if (P2C) {
+            x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
+            x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
+          }
+          x0 = (e < nvalid) ? x0 : -CUDART_INF_F;
+          x1 = (e + 1 < nvalid) ? x1 : -CUDART_INF_F;
+          s[e] = x0; s[e + 1] = x1;
+          mx = fmaxf(mx, fmaxf(x0, x1));
+          const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
+          lsum += a + b;
+          pk[e / 2] = pack_bf16x2(a, b);
         }
       }
       // row maximum over the four threads of the row
@@ -449,8 +478,21 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       TL0(13000 + it);
 #pragma unroll
       for (int g = 0; g < GROUPS; ++g) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(g * BQ + row_t)));
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = ex2(m_run - m_new);
+      const float row_max = mx * sl2;                                  // sl2 > 0
+      const float excess = row_max - m_prev;
+      const bool redo = (excess > 8.f) || (it == 0 && excess < -64.f);
+      float m_new = m_prev, alpha = 1.f;
+      if (redo) {
+        m_new = row_max;
+        alpha = ex2(m_prev - m_new);
+        lsum = 0.f;
+#pragma unroll
+        for (int e = 0; e < KPT; e += 2) {
+          const float a = ex2(fmaf(s[e], sl2, -m_new)), b = ex2(fmaf(s[e + 1], sl2, -m_new));
+          lsum += a + b;
+          pk[e / 2] = pack_bf16x2(a, b);
+        }
+      }
       if (it > 0) {
         wait(O_FULL, (uint32_t)((it - 1) & 1));
         tc_fence_after();
@@ -464,15 +506,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         }
       }
       TL0(14000 + it);
-      float lsum = 0.f;
-      uint32_t pk[KPT / 2];
-#pragma unroll
-      for (int e = 0; e < KPT; e += 2) {
-        float a = ex2(s[e] - m_new), b = ex2(s[e + 1] - m_new);
-        lsum += a + b;
-        pk[e / 2] = pack_bf16x2(a, b);
-      }
-      l_part = l_part * alpha + lsum;
+      l_part = (it > 0 ? l_part * alpha : 0.f) + lsum;
       m_run = m_new;
       tmem_st16(tP, pk);
       tmem_st_wait();
@@ -480,9 +514,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(P_READY));
       TL0(15000 + it);
-      bar_all_cuda_warps();                                            // staging rows and the exchange buffer are free again
+      bar_all_cuda_warps();                                            // p2c staging rows and the exchange buffer are free again
       TL0(16000 + it);
-      if (it + 1 < n_kv) drain_tile();
+      if (it + 1 < n_kv) drain_p2();
       TL0(17000 + it);
       bar_all_cuda_warps();                                            // staging of the next tile is complete
       TL0(18000 + it);
