@@ -41,13 +41,15 @@ constexpr int GROUPS = 4;                       // threads per query row
 constexpr int KPT = BK / GROUPS;                // keys per thread in the softmax (32)
 constexpr int NCW = 4 * GROUPS;                 // CUDA-core warps
 constexpr int NCT = NCW * 32;                   // CUDA-core threads
-constexpr int NTHREADS = (NCW + 2) * 32;
+constexpr int NTHREADS = (NCW + 3) * 32;       // + TMA producer warp, MMA warp, scheduler warp
 constexpr int STG_STRIDE = 336;                 // bytes per staging row: 160 bf16 + 16 pad (odd multiple of 16)
 constexpr int STG_COLS = 160;
 constexpr uint32_t OFF_Q = 0, OFF_K = 16384, OFF_V = 32768, OFF_KR = 49152, OFF_QR = 81920;
 constexpr uint32_t OFF_STC = 114688, OFF_STP = OFF_STC + BQ * STG_STRIDE, OFF_XCH = OFF_STP + BK * STG_STRIDE;
 constexpr uint32_t OFF_BAR = OFF_XCH + GROUPS * BQ * 4;
-constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;   // + slack for the 1024-byte alignment of the base
+constexpr uint32_t OFF_WORK = OFF_BAR + 256;        // ring of work items published by the scheduler lane
+constexpr uint32_t OFF_CUR = OFF_WORK + 256;        // the CUDA-core warps' agreed copy of their current item
+constexpr uint32_t SMEM_BYTES = OFF_CUR + 64 + 1024;   // + slack for the 1024-byte alignment of the base
 static_assert(OFF_STP % 16 == 0 && OFF_XCH % 16 == 0 && OFF_BAR % 16 == 0, "offsets must stay 16-byte aligned");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
@@ -55,8 +57,12 @@ constexpr uint32_t TM_S = 0, TM_O = 128, TM_RING = 192, TM_P = 448, TM_COLS = 51
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per wait, then give up
 
 enum Bar { Q_FULL = 0, K_FULL, K_EMPTY, V_FULL, V_EMPTY, KR_FULL, KR_EMPTY, QR_FULL, QR_EMPTY,
-           S_FULL, S_TAKEN, RING_FULL_A, RING_FULL_B, RING_FREE_A, RING_FREE_B, P_READY, O_FULL, DONE, NBARS };
-static_assert(NBARS * 8 <= 160, "barrier block");
+           S_FULL, S_TAKEN, RING_FULL_A, RING_FULL_B, RING_FREE_A, RING_FREE_B, P_READY, O_FULL,
+           Q_EMPTY, O_TAKEN, DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
+           WORK_EMPTY0, WORK_EMPTY1, WORK_EMPTY2, WORK_EMPTY3, NBARS };
+constexpr int WORK_RING = 4;
+constexpr int WORK_READERS = 3 + 1 + NCW;       // three producer lanes, the MMA lane, one lane per CUDA-core warp
+static_assert(NBARS * 8 <= 256, "barrier block");
 
 struct TileListHeader { int32_t n_tiles; int32_t pad[3]; };
 
@@ -67,7 +73,7 @@ __device__ long long g_timeline[3][TL_MAX][2];
 __device__ int g_timeline_n[3];
 #define TDB_TL(role, evt)                                                                     \
   do {                                                                                        \
-    if (blockIdx.x == (TDB_TIMELINE) && blockIdx.y == 0 && tl_n[role] < TL_MAX) {             \
+    if (blockIdx.x == (TDB_TIMELINE) && tl_n[role] < TL_MAX) {             \
       g_timeline[role][tl_n[role]][0] = (evt);                                                \
       g_timeline[role][tl_n[role]][1] = clock64();                                            \
       g_timeline_n[role] = ++tl_n[role];                                                      \
@@ -152,6 +158,33 @@ __device__ __forceinline__ void drain_chunk(uint32_t taddr, uint32_t dst_saddr) 
   }
 }
 
+// One unit of work: a 128-query tile of one sequence for one head.
+struct Work {
+  int q0, len, rows, bcoord, h, n_kv;      // n_kv == 0: tile of padded query rows only (zeros, no tensor work)
+  int64_t tok0;
+};
+
+__device__ __forceinline__ bool get_work(const AttnParams& p, int total_tiles, int w, Work& k) {
+  const int tile = w / p.H;
+  if (tile >= total_tiles) return false;
+  k.h = w - tile * p.H;
+  if (p.varlen) {
+    const int32_t* ws = reinterpret_cast<const int32_t*>(p.workspace);
+    const int2 e = reinterpret_cast<const int2*>(ws + 4)[tile];
+    const int c0 = p.cu_seqlens[e.x];
+    k.len = p.cu_seqlens[e.x + 1] - c0; k.rows = k.len; k.tok0 = c0; k.bcoord = 0; k.q0 = e.y;
+  } else {
+    const int qtiles = (p.L + BQ - 1) / BQ;
+    const int seq = tile / qtiles;
+    k.q0 = (tile - seq * qtiles) * BQ;
+    int len = p.seqlens ? p.seqlens[seq] : p.L;
+    k.len = len < 0 ? 0 : (len > p.L ? p.L : len);
+    k.rows = p.L; k.tok0 = 0; k.bcoord = seq;
+  }
+  k.n_kv = k.q0 < k.len ? (k.len + BK - 1) / BK : 0;
+  return true;
+}
+
 template <bool C2P, bool P2C>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -159,42 +192,18 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
                  const __grid_constant__ CUtensorMap tm_qr) {
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.y;
 
-  // ---- which tile --------------------------------------------------------------------------
-  int seq, q0, len, rows, bcoord; int64_t tok0;
-  if (p.varlen) {
-    const int32_t* ws = reinterpret_cast<const int32_t*>(p.workspace);
-    if ((int)blockIdx.x >= ws[0]) return;
-    int2 e = reinterpret_cast<const int2*>(ws + 4)[blockIdx.x];
-    seq = e.x; q0 = e.y;
-    int c0 = p.cu_seqlens[seq];
-    len = p.cu_seqlens[seq + 1] - c0; rows = len; tok0 = c0; bcoord = 0;
-  } else {
-    int qtiles = (p.L + BQ - 1) / BQ;
-    seq = blockIdx.x / qtiles; q0 = (blockIdx.x % qtiles) * BQ;
-    len = p.seqlens ? p.seqlens[seq] : p.L;
-    len = len < 0 ? 0 : (len > p.L ? p.L : len);
-    rows = p.L; tok0 = 0; bcoord = seq;
-  }
-  __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)bcoord * p.o_sb + (tok0 + q0) * p.o_st + (int64_t)h * p.o_sh;
-  if (q0 >= len) {                       // tile of padded query rows only: zeros, no tensor work
-    if (tid < BQ && q0 + tid < rows) {
-      uint4 z = make_uint4(0, 0, 0, 0);
-      uint4* dst = reinterpret_cast<uint4*>(obase + (int64_t)tid * p.o_st);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) dst[i] = z;
-      if (p.lse) p.lse[(int64_t)bcoord * p.lse_sb + (int64_t)h * p.lse_sh + tok0 + q0 + tid] = 0.f;
-    }
-    return;
-  }
+  // Persistent CTA.  Work items (query tile x head) are handed out by a device-wide counter (status word 2), so a
+  // CTA that drew short sequences simply draws more of them; a scheduler lane publishes each item in a small
+  // shared-memory ring that every role reads in the same order.
+  const int total_tiles = p.varlen ? reinterpret_cast<const int32_t*>(p.workspace)[0]
+                                   : p.n_seqs * ((p.L + BQ - 1) / BQ);
   {                                      // an earlier CTA gave up: do not start (decided once per CTA)
     __shared__ int s_skip;
     if (tid == 0) s_skip = (*reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
     __syncthreads();
     if (s_skip) return;
   }
-  const int n_kv = (len + BK - 1) / BK;
 #ifdef TDB_TIMELINE
   int tl_n[3] = {0, 0, 0};
 #endif
@@ -205,16 +214,18 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   const uint32_t sQ = sbase + OFF_Q, sK = sbase + OFF_K, sV = sbase + OFF_V, sKr = sbase + OFF_KR, sQr = sbase + OFF_QR;
   const uint32_t stC = sbase + OFF_STC, stP = sbase + OFF_STP, sX = sbase + OFF_XCH;
   const uint32_t bars = sbase + OFF_BAR;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_BAR + 160);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_BAR + 168);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_BAR + 232);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_BAR + 240);
+  Work* work_ring = reinterpret_cast<Work*>(gbase + OFF_WORK);
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
   auto wait = [&](int i, uint32_t parity) { return mbar_wait(bar(i), parity, abort_flag, p.status, 1 + i, WAIT_LIMIT_NS); };
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < NBARS; ++i) {
-      const bool by_warps = (i == S_TAKEN || i == RING_FREE_A || i == RING_FREE_B || i == P_READY);
-      mbar_init(bar(i), by_warps ? (uint32_t)NCW : 1u);
+      const bool by_warps = (i == S_TAKEN || i == RING_FREE_A || i == RING_FREE_B || i == P_READY || i == O_TAKEN);
+      const bool by_readers = (i >= WORK_EMPTY0 && i <= WORK_EMPTY3);
+      mbar_init(bar(i), by_readers ? (uint32_t)WORK_READERS : (by_warps ? (uint32_t)NCW : 1u));
     }
     fence_mbar_init();
   }
@@ -232,47 +243,116 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  // Item n of this CTA's stream; n_kv < 0 marks the end of the stream.  (Tiles that consist of padded query rows
+  // only never enter the ring: the scheduler warp zeroes them itself.)
+  auto fetch = [&](int n, Work& k) {
+    wait(WORK_FULL0 + (n % WORK_RING), (uint32_t)((n / WORK_RING) & 1));
+    k = work_ring[n % WORK_RING];
+    if (*abort_flag) k.n_kv = -1;
+    return k.n_kv > 0;
+  };
+  auto release = [&](int n) { mbar_arrive(bar(WORK_EMPTY0 + (n % WORK_RING))); };
+  auto next_tensor_item = [&](int& n, Work& k) { return fetch(n, k); };
+
   if (warp == NCW) {
     // ================================ TMA producers ==========================================
-    if (lane == 0) {                       // relative tables and K
-      for (int it = 0; it < n_kv; ++it) {
-        const int k0 = it * BK;
-        const uint32_t pe = (uint32_t)((it - 1) & 1);
-        int x0 = q0 - k0 - (BK - 1) + p.exp_delta_max;
-        x0 = x0 < 0 ? 0 : (x0 > p.exp_rows - BAND ? p.exp_rows - BAND : x0);
-        if (C2P) {
-          if (it > 0) wait(KR_EMPTY, pe);
-          if (!*abort_flag) {
-            mbar_expect_tx(bar(KR_FULL), BAND * HD * 2);
-            tma_load_3d(sKr, &tm_kr, bar(KR_FULL), 0, x0, h);
+    if (lane == 0) {                       // relative tables and K, once per key tile
+      Work k;
+      int g = 0, n = 0;
+      while (next_tensor_item(n, k)) {
+        for (int it = 0; it < k.n_kv; ++it, ++g) {
+          const int k0 = it * BK;
+          const uint32_t pe = (uint32_t)((g - 1) & 1);
+          int x0 = k.q0 - k0 - (BK - 1) + p.exp_delta_max;
+          x0 = x0 < 0 ? 0 : (x0 > p.exp_rows - BAND ? p.exp_rows - BAND : x0);
+          if (C2P) {
+            if (g > 0) wait(KR_EMPTY, pe);
+            if (!*abort_flag) {
+              mbar_expect_tx(bar(KR_FULL), BAND * HD * 2);
+              tma_load_3d(sKr, &tm_kr, bar(KR_FULL), 0, x0, k.h);
+            }
           }
-          TDB_TL(2, 100 + it);
-        }
-        if (it > 0) wait(K_EMPTY, pe);
-        if (!*abort_flag) {
-          mbar_expect_tx(bar(K_FULL), BK * HD * 2);
-          tma_load_4d(sK, &tm_k, bar(K_FULL), 0, (int)(tok0 + k0), h, bcoord);
-        }
-        TDB_TL(2, 200 + it);
-        if (P2C) {
-          if (it > 0) wait(QR_EMPTY, pe);
+          if (g > 0) wait(K_EMPTY, pe);
           if (!*abort_flag) {
-            mbar_expect_tx(bar(QR_FULL), BAND * HD * 2);
-            tma_load_3d(sQr, &tm_qr, bar(QR_FULL), 0, x0, h);
+            mbar_expect_tx(bar(K_FULL), BK * HD * 2);
+            tma_load_4d(sK, &tm_k, bar(K_FULL), 0, (int)(k.tok0 + k0), k.h, k.bcoord);
           }
-          TDB_TL(2, 300 + it);
+          if (P2C) {
+            if (g > 0) wait(QR_EMPTY, pe);
+            if (!*abort_flag) {
+              mbar_expect_tx(bar(QR_FULL), BAND * HD * 2);
+              tma_load_3d(sQr, &tm_qr, bar(QR_FULL), 0, x0, k.h);
+            }
+          }
+          TDB_TL(2, 100 + g);
         }
+        release(n);
+        ++n;
       }
-    } else if (lane == 1) {                // Q once, then V
-      mbar_expect_tx(bar(Q_FULL), BQ * HD * 2);
-      tma_load_4d(sQ, &tm_q, bar(Q_FULL), 0, (int)(tok0 + q0), h, bcoord);
-      for (int it = 0; it < n_kv; ++it) {
-        if (it > 0) wait(V_EMPTY, (uint32_t)((it - 1) & 1));
+      release(n);
+    } else if (lane == 1) {                // V, once per key tile
+      Work k;
+      int g = 0, n = 0;
+      while (next_tensor_item(n, k)) {
+        for (int it = 0; it < k.n_kv; ++it, ++g) {
+          if (g > 0) wait(V_EMPTY, (uint32_t)((g - 1) & 1));
+          if (!*abort_flag) {
+            mbar_expect_tx(bar(V_FULL), BK * HD * 2);
+            tma_load_4d(sV, &tm_v, bar(V_FULL), 0, (int)(k.tok0 + it * BK), k.h, k.bcoord);
+          }
+        }
+        release(n);
+        ++n;
+      }
+      release(n);
+    } else if (lane == 2) {                // Q, once per work item
+      Work k;
+      int n = 0, m = 0;                    // m counts items with tensor work
+      while (next_tensor_item(n, k)) {
+        if (m > 0) wait(Q_EMPTY, (uint32_t)((m - 1) & 1));
         if (!*abort_flag) {
-          mbar_expect_tx(bar(V_FULL), BK * HD * 2);
-          tma_load_4d(sV, &tm_v, bar(V_FULL), 0, (int)(tok0 + it * BK), h, bcoord);
+          mbar_expect_tx(bar(Q_FULL), BQ * HD * 2);
+          tma_load_4d(sQ, &tm_q, bar(Q_FULL), 0, (int)(k.tok0 + k.q0), k.h, k.bcoord);
         }
+        TDB_TL(2, 900 + m);
+        ++m;
+        release(n);
+        ++n;
       }
+      release(n);
+    }
+  } else if (warp == NCW + 2) {
+    // ================================ scheduler ==============================================
+    // Draws work items from the device-wide counter and publishes those with tensor work in the ring; tiles made of
+    // padded query rows only (padded form) are zeroed here by the whole warp and never reach the other roles.
+    int n = 0;
+    while (true) {
+      int w = 0;
+      if (lane == 0) w = *abort_flag ? 0x7fffffff : atomicAdd(p.status + 2, 1);
+      w = __shfl_sync(0xffffffffu, w, 0);
+      Work k;
+      if (!get_work(p, total_tiles, w, k)) k.n_kv = -1;
+      if (k.n_kv == 0) {
+        for (int r = lane; r < BQ; r += 32) {
+          if (k.q0 + r >= k.rows) break;
+          __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)k.bcoord * p.o_sb +
+                              (k.tok0 + k.q0 + r) * p.o_st + (int64_t)k.h * p.o_sh;
+          uint4* dst = reinterpret_cast<uint4*>(ob);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          if (p.lse) p.lse[(int64_t)k.bcoord * p.lse_sb + (int64_t)k.h * p.lse_sh + k.tok0 + k.q0 + r] = 0.f;
+        }
+        continue;
+      }
+      const int slot = n % WORK_RING;
+      if (lane == 0) {
+        if (n >= WORK_RING) wait(WORK_EMPTY0 + slot, (uint32_t)(((n / WORK_RING) - 1) & 1));
+        work_ring[slot] = k;
+        mbar_arrive(bar(WORK_FULL0 + slot));         // release: the item is visible to whoever observes the phase
+      }
+      __syncwarp();
+      ++n;
+      if (k.n_kv < 0) break;
     }
   } else if (warp == NCW + 1) {
     // ================================ MMA issuer ============================================
@@ -298,72 +378,84 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_commit(bar(half ? RING_FULL_B : RING_FULL_A));
         ++fills[half];
       };
-      auto issue_c = [&](int t) {          // content->position band of key tile t: one 256-column product into both slots
-        wait(KR_FULL, (uint32_t)(t & 1));
-        TDB_TL(1, 1000 + t);
-        if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
-        if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
-        tc_fence_after();
+      // The three products of key tile g (global count) that do not depend on the softmax of an earlier tile.
+      auto issue_scores = [&](int g) {
+        const uint32_t ph = (uint32_t)(g & 1);
+        if (C2P) {                         // content->position band: one 256-column product into both slots
+          wait(KR_FULL, ph);
+          if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
+          if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQ + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
-        tc_commit(bar(RING_FULL_A));
-        tc_commit(bar(RING_FULL_B));
-        tc_commit(bar(KR_EMPTY));
-        ++fills[0]; ++fills[1];
-        TDB_TL(1, 1200 + t);
-      };
-      auto issue_s = [&](int t) {          // content score of key tile t
-        wait(K_FULL, (uint32_t)(t & 1));
-        if (t > 0) wait(S_TAKEN, (uint32_t)((t - 1) & 1));
+          for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQ + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
+          tc_commit(bar(RING_FULL_A));
+          tc_commit(bar(RING_FULL_B));
+          tc_commit(bar(KR_EMPTY));
+          ++fills[0]; ++fills[1];
+          TDB_TL(1, 1000 + g);
+        }
+        wait(K_FULL, ph);                  // content score
+        if (g > 0) wait(S_TAKEN, (uint32_t)((g - 1) & 1));
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQ + 2 * k, dK + 2 * k, ID_S, k > 0);
         tc_commit(bar(S_FULL));
-        TDB_TL(1, 2000 + t);
-      };
-      auto issue_p2 = [&](int t) {         // position->content band of key tile t; releases K afterwards
-        if (P2C) {
-          wait(QR_FULL, (uint32_t)(t & 1));
-          TDB_TL(1, 3000 + t);
+        TDB_TL(1, 2000 + g);
+        if (P2C) {                         // position->content band, each half as soon as its slot is drained of c2p
+          wait(QR_FULL, ph);
           band_half(dK, dQr, 0);
-          TDB_TL(1, 3100 + t);
           band_half(dK, dQr, 1);
           tc_commit(bar(QR_EMPTY));
         }
         tc_commit(bar(K_EMPTY));
-        TDB_TL(1, 3200 + t);
+        TDB_TL(1, 3000 + g);
       };
 
-      TDB_TL(1, 1);
-      wait(Q_FULL, 0);
-      TDB_TL(1, 2);
-      if (C2P) issue_c(0);
-      issue_s(0);
-      issue_p2(0);
-      for (int it = 0; it < n_kv; ++it) {
-        const uint32_t ph = (uint32_t)(it & 1);
-        if (it + 1 < n_kv) {
-          if (C2P) issue_c(it + 1);        // runs while the CUDA warps are in the softmax of tile `it`
-          issue_s(it + 1);
-          issue_p2(it + 1);                // each half starts as soon as its ring slot has been drained of C
-        }
-        wait(V_FULL, ph);
-        TDB_TL(1, 4000 + it);
-        wait(P_READY, ph);
-        TDB_TL(1, 4100 + it);
-        tc_fence_after();
+      Work cur, nx;
+      int n = 0, g = 0, n_item = 0, it = 0;
+      if (next_tensor_item(n, cur)) {
+        wait(Q_FULL, 0);
+        issue_scores(0);
+        if (cur.n_kv == 1) tc_commit(bar(Q_EMPTY));
+        while (true) {
+          // look ahead: the key tile after (cur, it), possibly the first one of the next work item
+          bool has_next = true, new_item = false;
+          int n_next = n;
+          if (it + 1 >= cur.n_kv) {
+            new_item = true;
+            n_next = n + 1;
+            has_next = next_tensor_item(n_next, nx);
+          }
+          if (has_next) {
+            if (new_item) wait(Q_FULL, (uint32_t)((n_item + 1) & 1));
+            issue_scores(g + 1);           // runs while the CUDA warps work on key tile g
+            const bool last_of_item = new_item ? (nx.n_kv == 1) : (it + 2 == cur.n_kv);
+            if (last_of_item) tc_commit(bar(Q_EMPTY));
+          }
+          wait(V_FULL, (uint32_t)(g & 1));
+          wait(P_READY, (uint32_t)(g & 1));
+          if (it == 0 && n_item > 0) wait(O_TAKEN, (uint32_t)((n_item - 1) & 1));
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k)
-          mma_ts(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (it > 0 || k > 0) ? 1u : 0u);
-        tc_commit(bar(O_FULL));
-        tc_commit(bar(V_EMPTY));
-        TDB_TL(1, 4200 + it);
+          for (int k = 0; k < BK / 16; ++k)
+            mma_ts(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (it > 0 || k > 0) ? 1u : 0u);
+          tc_commit(bar(O_FULL));
+          tc_commit(bar(V_EMPTY));
+          TDB_TL(1, 4000 + g);
+          if (new_item) {                  // done with the current item (and with the end marker, if that is what follows)
+            release(n);
+            n = n_next;
+          }
+          if (!has_next) break;
+          ++g;
+          if (new_item) { cur = nx; it = 0; ++n_item; } else { ++it; }
+        }
       }
+      release(n);                          // the end-of-stream marker
       // Everything issued above must have retired before tensor memory is released.
       tc_commit(bar(DONE));
       int never = 0;                       // this wait runs even after an abort, with its own limit
       mbar_wait(bar(DONE), 0, &never, p.status, 1 + DONE, WAIT_LIMIT_NS);
-      TDB_TL(1, 9);
     }
   } else {
     // ================================ drain + softmax + epilogue ============================
@@ -381,7 +473,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     const uint32_t c_read = c_row + 2u * (uint32_t)(lane + (BK - 1) - KPT * grp);          // key e of this thread: c_read - 2e
     const uint32_t p_read = stP + (uint32_t)(KPT * grp) * STG_STRIDE + 2u * (uint32_t)(row_t + 31);  // + e*STRIDE - 2e
     const uint32_t x_mine = sX + 4u * (uint32_t)(grp * BQ + row_t);
-    float m_run = -CUDART_INF_F, l_part = 0.f;
     int drains[2] = {0, 0};
 
     // Drain one band half from ring slot `half`.  kind 0: c2p (window starts at 32*qd), kind 1: p2c (96 - 32*qd).
@@ -402,154 +493,186 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
 
 #define TL0(evt) do { if (tid == 0) TDB_TL(0, evt); } while (0)
     TL0(1);
-    drain_c();                                                         // bands of key tile 0
-    drain_p2();
-    TL0(2);
-    bar_all_cuda_warps();
-    TL0(3);
-
-    for (int it = 0; it < n_kv; ++it) {
-      const uint32_t ph = (uint32_t)(it & 1);
-      const int nvalid = len - it * BK - KPT * grp;                    // keys e >= nvalid of this thread are masked
-      TL0(10000 + it);
-      wait(S_FULL, ph);
-      TL0(11000 + it);
-      tc_fence_after();
-      float s[KPT];
+    struct CurItem { Work k; int has_next; };
+    volatile CurItem* cur_shared = reinterpret_cast<volatile CurItem*>(gbase + OFF_CUR);
+    Work cur;
+    int g = 0, n_item = 0;
+    for (int n = 0;; ++n) {
+      // One thread reads the ring (this item, and whether another one follows); everybody else takes its copy
+      // after the barrier, so that all 16 warps agree on the trip counts below even after an abort.
+      if (tid == 0) {
+        Work k, nk;
+        fetch(n, k);
+        const bool more = k.n_kv > 0 && fetch(n + 1, nk);
+        CurItem* c = const_cast<CurItem*>(cur_shared);
+        c->k = k;
+        c->has_next = more ? 1 : 0;
+      }
+      bar_all_cuda_warps();
       {
-        uint32_t* sr = reinterpret_cast<uint32_t*>(s);
-        tmem_ld32(tS, sr);
-        tmem_ld_wait32(sr);
+        const CurItem* c = const_cast<const CurItem*>(cur_shared);
+        cur = c->k;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(S_TAKEN));
-      // Phase 1: add the content->position term, then hand the c2p staging rows (shared only inside the
-      // quadrant) to the next key tile at once, so that its position->content products can run during phase 2.
-      if (C2P) {
-#pragma unroll
-        for (int e = 0; e < KPT; ++e) s[e] += lds_bf16(c_read - 2u * e);
-        TL0(11500 + it);
-        bar_quadrant(qd);
-        if (it + 1 < n_kv) drain_c();
-        TL0(11800 + it);
+      const bool item_follows = cur_shared->has_next != 0;
+      if (cur.n_kv <= 0) {
+        if (lane == 0) release(n);
+        break;
       }
-      // Phase 2.  Scores stay unscaled in s[]; the exponentials are taken at once against the reference exponent of the
-      // previous tiles (0 on the first tile) so that the MUFU work overlaps the shared-memory reads, and are
-      // redone only for rows whose new maximum is more than 2^8 above (or, on the first tile, 2^64 below) it.
-      const float m_prev = (it > 0) ? m_run : 0.f;
-      float mx = -CUDART_INF_F, lsum = 0.f;
-      uint32_t pk[KPT / 2];
-      if (nvalid >= KPT) {
-#pragma unroll
-        for (int e = 0; e < KPT; e += 2) {
-          float x0 = s[e], x1 = s[e + 1];
-          if (P2C) {
-            x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
-            x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
-          }
-          s[e] = x0; s[e + 1] = x1;
-          mx = fmaxf(mx, fmaxf(x0, x1));
-          const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
-          lsum += a + b;
-          pk[e / 2] = pack_bf16x2(a, b);
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < KPT; e += 2) {
-          float x0 = s[e], x1 = s[e + 1];
-          if (P2C) {
-            x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
-            x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
-          }
-          x0 = (e < nvalid) ? x0 : -CUDART_INF_F;
-          x1 = (e + 1 < nvalid) ? x1 : -CUDART_INF_F;
-          s[e] = x0; s[e + 1] = x1;
-          mx = fmaxf(mx, fmaxf(x0, x1));
-          const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
-          lsum += a + b;
-          pk[e / 2] = pack_bf16x2(a, b);
-        }
+      if (n == 0) {                                                    // bands of the very first key tile
+        drain_c();
+        drain_p2();
+        bar_all_cuda_warps();
       }
-      // row maximum over the four threads of the row
-      TL0(12000 + it);
-      sts_f32(x_mine, mx);
-      bar_quadrant(qd);
-      TL0(13000 + it);
-#pragma unroll
-      for (int g = 0; g < GROUPS; ++g) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(g * BQ + row_t)));
-      const float row_max = mx * sl2;                                  // sl2 > 0
-      const float excess = row_max - m_prev;
-      const bool redo = (excess > 8.f) || (it == 0 && excess < -64.f);
-      float m_new = m_prev, alpha = 1.f;
-      if (redo) {
-        m_new = row_max;
-        alpha = ex2(m_prev - m_new);
-        lsum = 0.f;
-#pragma unroll
-        for (int e = 0; e < KPT; e += 2) {
-          const float a = ex2(fmaf(s[e], sl2, -m_new)), b = ex2(fmaf(s[e + 1], sl2, -m_new));
-          lsum += a + b;
-          pk[e / 2] = pack_bf16x2(a, b);
-        }
-      }
-      if (it > 0) {
-        wait(O_FULL, (uint32_t)((it - 1) & 1));
+      float m_run = 0.f, l_part = 0.f;
+      for (int it = 0; it < cur.n_kv; ++it, ++g) {
+        const bool has_next = (it + 1 < cur.n_kv) || item_follows;
+        const int nvalid = cur.len - it * BK - KPT * grp;            // keys e >= nvalid of this thread are masked
+        TL0(10000 + g);
+        wait(S_FULL, (uint32_t)(g & 1));
+        TL0(11000 + g);
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          uint32_t r[16];
-          tmem_ld16(tO, r);
-          tmem_ld_wait16(r);
-#pragma unroll
-          for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-          tmem_st16(tO, r);
+        float s[KPT];
+        {
+          uint32_t* sr = reinterpret_cast<uint32_t*>(s);
+          tmem_ld32(tS, sr);
+          tmem_ld_wait32(sr);
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(S_TAKEN));
+        // Phase 1: add the content->position term, then hand the c2p staging rows (shared only inside the
+        // quadrant) to the next key tile at once, so that its position->content products can run during phase 2.
+        if (C2P) {
+#pragma unroll
+          for (int e = 0; e < KPT; ++e) s[e] += lds_bf16(c_read - 2u * e);
+          TL0(11500 + g);
+          bar_quadrant(qd);
+          if (has_next) drain_c();
+          TL0(11800 + g);
+        }
+        // Phase 2.  Scores stay unscaled in s[]; the exponentials are taken at once against the reference exponent
+        // of the previous tiles (0 on the first tile) so that the MUFU work overlaps the shared-memory reads, and
+        // are redone only for rows whose new maximum is more than 2^8 above (or, on the first tile, 2^64 below) it.
+        const float m_prev = (it > 0) ? m_run : 0.f;
+        float mx = -CUDART_INF_F, lsum = 0.f;
+        uint32_t pk[KPT / 2];
+        if (nvalid >= KPT) {
+#pragma unroll
+          for (int e = 0; e < KPT; e += 2) {
+            float x0 = s[e], x1 = s[e + 1];
+            if (P2C) {
+              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
+              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
+            }
+            s[e] = x0; s[e + 1] = x1;
+            mx = fmaxf(mx, fmaxf(x0, x1));
+            const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
+            lsum += a + b;
+            pk[e / 2] = pack_bf16x2(a, b);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < KPT; e += 2) {
+            float x0 = s[e], x1 = s[e + 1];
+            if (P2C) {
+              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
+              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
+            }
+            x0 = (e < nvalid) ? x0 : -CUDART_INF_F;
+            x1 = (e + 1 < nvalid) ? x1 : -CUDART_INF_F;
+            s[e] = x0; s[e + 1] = x1;
+            mx = fmaxf(mx, fmaxf(x0, x1));
+            const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
+            lsum += a + b;
+            pk[e / 2] = pack_bf16x2(a, b);
+          }
+        }
+        // row maximum over the four threads of the row
+        TL0(12000 + g);
+        sts_f32(x_mine, mx);
+        bar_quadrant(qd);
+        TL0(13000 + g);
+#pragma unroll
+        for (int gg = 0; gg < GROUPS; ++gg) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t)));
+        const float row_max = mx * sl2;                                // sl2 > 0
+        const float excess = row_max - m_prev;
+        const bool redo = (excess > 8.f) || (it == 0 && excess < -64.f);
+        float m_new = m_prev, alpha = 1.f;
+        if (redo) {
+          m_new = row_max;
+          alpha = ex2(m_prev - m_new);
+          lsum = 0.f;
+#pragma unroll
+          for (int e = 0; e < KPT; e += 2) {
+            const float a = ex2(fmaf(s[e], sl2, -m_new)), b = ex2(fmaf(s[e + 1], sl2, -m_new));
+            lsum += a + b;
+            pk[e / 2] = pack_bf16x2(a, b);
+          }
+        }
+        if (it > 0) {
+          wait(O_FULL, (uint32_t)((g - 1) & 1));
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            uint32_t r[16];
+            tmem_ld16(tO, r);
+            tmem_ld_wait16(r);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st16(tO, r);
+          }
+        }
+        TL0(14000 + g);
+        l_part = (it > 0 ? l_part * alpha : 0.f) + lsum;
+        m_run = m_new;
+        tmem_st16(tP, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_READY));
+        TL0(15000 + g);
+        bar_all_cuda_warps();                                          // p2c staging rows and the exchange buffer are free again
+        TL0(16000 + g);
+        if (has_next) drain_p2();
+        TL0(17000 + g);
+        bar_all_cuda_warps();                                          // staging of the next key tile is complete
+        TL0(18000 + g);
       }
-      TL0(14000 + it);
-      l_part = (it > 0 ? l_part * alpha : 0.f) + lsum;
-      m_run = m_new;
-      tmem_st16(tP, pk);
-      tmem_st_wait();
+      // ---- epilogue of the work item: O / l -> global ----
+      sts_f32(x_mine, l_part);
+      bar_quadrant(qd);
+      float l_tot = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < GROUPS; ++gg) l_tot += lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t));
+      wait(O_FULL, (uint32_t)((g - 1) & 1));
+      TL0(20000 + n_item);
+      tc_fence_after();
+      uint32_t r[16];
+      tmem_ld16(tO, r);
+      tmem_ld_wait16(r);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_READY));
-      TL0(15000 + it);
-      bar_all_cuda_warps();                                            // p2c staging rows and the exchange buffer are free again
-      TL0(16000 + it);
-      if (it + 1 < n_kv) drain_p2();
-      TL0(17000 + it);
-      bar_all_cuda_warps();                                            // staging of the next tile is complete
-      TL0(18000 + it);
-    }
-    // ---- epilogue: O / l -> global ----
-    sts_f32(x_mine, l_part);
-    bar_quadrant(qd);
-    float l_tot = 0.f;
+      if (lane == 0) mbar_arrive(bar(O_TAKEN));                        // the next item's first P.V may overwrite O
+      const int row = cur.q0 + row_t;
+      const float inv = 1.f / l_tot;
+      if (row < cur.rows) {
+        const bool valid = row < cur.len;
+        uint32_t outw[8];
 #pragma unroll
-    for (int g = 0; g < GROUPS; ++g) l_tot += lds_f32(sX + 4u * (uint32_t)(g * BQ + row_t));
-    wait(O_FULL, (uint32_t)((n_kv - 1) & 1));
-    TL0(20000);
-    tc_fence_after();
-    const int row = q0 + row_t;
-    const float inv = 1.f / l_tot;
-    uint32_t r[16];
-    tmem_ld16(tO, r);
-    tmem_ld_wait16(r);
-    tc_fence_before();
-    if (row < rows) {
-      const bool valid = row < len;
-      uint32_t outw[8];
-#pragma unroll
-      for (int e = 0; e < 16; e += 2)
-        outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
-      uint4* dst = reinterpret_cast<uint4*>(obase + (int64_t)row_t * p.o_st + (HD / GROUPS) * grp);
-      dst[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-      dst[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
-      if (p.lse && grp == 0)
-        p.lse[(int64_t)bcoord * p.lse_sb + (int64_t)h * p.lse_sh + tok0 + row] =
-            valid ? (m_run * 0.6931471805599453f + logf(l_tot)) : 0.f;
+        for (int e = 0; e < 16; e += 2)
+          outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)cur.bcoord * p.o_sb +
+                              (cur.tok0 + row) * p.o_st + (int64_t)cur.h * p.o_sh + (HD / GROUPS) * grp;
+        uint4* dst = reinterpret_cast<uint4*>(orow);
+        dst[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+        dst[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+        if (p.lse && grp == 0)
+          p.lse[(int64_t)cur.bcoord * p.lse_sb + (int64_t)cur.h * p.lse_sh + cur.tok0 + row] =
+              valid ? (m_run * 0.6931471805599453f + logf(l_tot)) : 0.f;
+      }
+      TL0(21000 + n_item);
+      ++n_item;
+      if (lane == 0) release(n);
     }
-    TL0(21000);
   }
 
   // ---- teardown ------------------------------------------------------------------------------
@@ -675,19 +798,24 @@ int launch_attn_umma(const AttnParams& p, cudaStream_t s) {
   if (p.flags & TDB_FLAG_P2C) { if ((rc = table_map(&maps[4], p.qr_exp, p.exp_rows, p.H, "qr_exp"))) return rc; }
   else maps[4] = maps[0];
 
-  dim3 grid;
+  // Persistent CTAs: one per SM (201 KB of shared memory and all 512 tensor-memory columns each), never more
+  // than there are work items (query tiles x heads).
+  int dev = 0, sms = 0;
+  if ((rc = cuda_fail(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
+  if ((rc = cuda_fail(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))) return rc;
+  int64_t tiles;
   if (p.varlen) {
-    int64_t cap = (p.total_tokens + BQ - 1) / BQ + p.n_seqs + 1;
-    if (cap > 0x7fffffff) { set_error("too many tiles"); return TDB_ERR_SHAPE; }
+    tiles = (p.total_tokens + BQ - 1) / BQ + p.n_seqs + 1;           // upper bound; the device list has the real count
+    if (tiles * p.H > 0x7fffffff) { set_error("too many tiles"); return TDB_ERR_SHAPE; }
     build_tile_list_kernel<<<1, 1024, 0, s>>>(p.cu_seqlens, p.n_seqs, p.total_tokens,
-                                              reinterpret_cast<int32_t*>(p.workspace), (int)cap, p.status);
+                                              reinterpret_cast<int32_t*>(p.workspace), (int)tiles, p.status);
     if ((rc = cuda_fail(cudaGetLastError(), "build_tile_list launch"))) return rc;
-    grid = dim3((unsigned)cap, (unsigned)p.H, 1);
   } else {
-    int64_t tiles = (int64_t)p.n_seqs * ((p.L + BQ - 1) / BQ);
-    if (tiles > 0x7fffffff) { set_error("too many tiles"); return TDB_ERR_SHAPE; }
-    grid = dim3((unsigned)tiles, (unsigned)p.H, 1);
+    tiles = (int64_t)p.n_seqs * ((p.L + BQ - 1) / BQ);
+    if (tiles * p.H > 0x7fffffff) { set_error("too many tiles"); return TDB_ERR_SHAPE; }
   }
+  const int64_t items = tiles * p.H;
+  dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
   const bool c2p = p.flags & TDB_FLAG_C2P, p2c = p.flags & TDB_FLAG_P2C;
   if (c2p && p2c) return launch_variant<true, true>(p, grid, maps, s);
   if (c2p) return launch_variant<true, false>(p, grid, maps, s);
