@@ -129,6 +129,11 @@ __device__ __forceinline__ float lds_bf16(uint32_t addr) {
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
   return __uint_as_float(((uint32_t)v) << 16);
 }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
@@ -358,26 +363,14 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     // ================================ MMA issuer ============================================
     if (lane == 0) {
       constexpr uint32_t ID_S = make_idesc_bf16(128, BK, 0);
-      constexpr uint32_t ID_HALF = make_idesc_bf16(128, HALF, 0);
       constexpr uint32_t ID_BAND = make_idesc_bf16(128, BAND, 0);
       constexpr uint32_t ID_PV = make_idesc_bf16(128, HD, 1);
-      constexpr uint64_t HALF_ROWS = (uint64_t)((HALF * HD * 2) >> 4);      // descriptor offset of the upper 128 table rows
       const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
       const uint64_t dKr = smem_desc_sw128(sKr), dQr = smem_desc_sw128(sQr);
       const uint32_t tS = tmem + TM_S, tO = tmem + TM_O, tP = tmem + TM_P;
       const uint32_t tRing[2] = {tmem + TM_RING, tmem + TM_RING + HALF};
       int fills[2] = {0, 0};               // how often each ring slot has been filled so far
 
-      // One band half: A (128 rows) x table rows [128*half, +128) -> ring slot `half`.
-      auto band_half = [&](uint64_t dA, uint64_t dTab, int half) {
-        if (fills[half] > 0) wait(half ? RING_FREE_B : RING_FREE_A, (uint32_t)((fills[half] - 1) & 1));
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tRing[half], dA + 2 * k, dTab + (uint64_t)half * HALF_ROWS + 2 * k, ID_HALF, k > 0);
-        tc_commit(bar(half ? RING_FULL_B : RING_FULL_A));
-        ++fills[half];
-      };
       // The three products of key tile g (global count) that do not depend on the softmax of an earlier tile.
       auto issue_scores = [&](int g) {
         const uint32_t ph = (uint32_t)(g & 1);
@@ -401,11 +394,17 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQ + 2 * k, dK + 2 * k, ID_S, k > 0);
         tc_commit(bar(S_FULL));
         TDB_TL(1, 2000 + g);
-        if (P2C) {                         // position->content band, each half as soon as its slot is drained of c2p
+        if (P2C) {                         // position->content band (rows = keys), once the c2p band has been drained
           wait(QR_FULL, ph);
-          band_half(dK, dQr, 0);
-          band_half(dK, dQr, 1);
+          if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
+          if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dK + 2 * k, dQr + 2 * k, ID_BAND, k > 0);
+          tc_commit(bar(RING_FULL_A));
+          tc_commit(bar(RING_FULL_B));
           tc_commit(bar(QR_EMPTY));
+          ++fills[0]; ++fills[1];
         }
         tc_commit(bar(K_EMPTY));
         TDB_TL(1, 3000 + g);
@@ -543,8 +542,21 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         // Phase 1: add the content->position term, then hand the c2p staging rows (shared only inside the
         // quadrant) to the next key tile at once, so that its position->content products can run during phase 2.
         if (C2P) {
+          // The 32 values sit at descending addresses from c_read; read them as 17 aligned 32-bit words and
+          // realign odd lanes with a funnel shift (half the shared-memory wavefronts of 16-bit loads).
+          {
+            const uint32_t lo_addr = (c_read - 2u * (KPT - 1)) & ~3u;
+            const uint32_t sh = (uint32_t)(lane & 1) * 16u;
+            uint32_t wv[KPT / 2 + 1];
 #pragma unroll
-          for (int e = 0; e < KPT; ++e) s[e] += lds_bf16(c_read - 2u * e);
+            for (int k = 0; k <= KPT / 2; ++k) wv[k] = lds_u32(lo_addr + 4u * k);
+#pragma unroll
+            for (int k = 0; k < KPT / 2; ++k) {
+              const uint32_t v = __funnelshift_r(wv[k], wv[k + 1], sh);       // (element 2k, element 2k+1) ascending
+              s[KPT - 1 - 2 * k] += __uint_as_float(v << 16);
+              s[KPT - 2 - 2 * k] += __uint_as_float(v & 0xffff0000u);
+            }
+          }
           TL0(11500 + g);
           bar_quadrant(qd);
           if (has_next) drain_c();
