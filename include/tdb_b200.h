@@ -68,9 +68,12 @@ TDB_API int tdb_bucket_table(int position_buckets, int max_relative_positions, i
 /* out[h, r, :] = rel[r, :] . W[h*D:(h+1)*D, :]^T + bias[h*D:(h+1)*D]      (r < two_span)
  * rel [two_span, hidden] (already LayerNorm'd by the encoder), W [H*D, hidden] row-major, bias [H*D] or NULL,
  * out [H, two_span, D]; all of `dtype`.  Replaces model.py:92-110 (key_proj/query_proj or
- * pos_key_proj/pos_query_proj applied to rel_embeddings followed by the head split at :70-73). */
+ * pos_key_proj/pos_query_proj applied to rel_embeddings followed by the head split at :70-73).
+ * bf16 with D == 64 runs as a tcgen05 GEMM (TMA-staged operands, accumulator in tensor memory); f32 runs on
+ * the CUDA cores with fp32 accumulation.  status: int32[4] zeroed device words as for the attention calls
+ * (word 0 reports a bounded wait that gave up); required for bf16, may be NULL for f32. */
 TDB_API int tdb_relpos_project(const void* rel, const void* W, const void* bias, int two_span, int hidden,
-                       int H, int D, int dtype, void* out, void* stream);
+                       int H, int D, int dtype, void* out, int32_t* status, void* stream);
 
 /* Distance-expanded copy of a projected table, always bf16:
  *   out[h, x, :] = table[h, idx[clamp(x - exp_delta_max, -idx_delta_max, idx_delta_max) + idx_delta_max], :]

@@ -38,7 +38,7 @@ def test_host_side_validation_needs_no_gpu():
     lib = _cabi.lib
     assert lib.tdb_bucket_table(256, 512, 100, None, None) == _cabi.ERR_ARG
     assert lib.tdb_bucket_table(256, 100, 100, 16, None) == _cabi.ERR_ARG       # max_pos <= buckets/2
-    assert lib.tdb_relpos_project(None, None, None, 1, 1, 1, 1, 0, None, None) == _cabi.ERR_ARG
+    assert lib.tdb_relpos_project(None, None, None, 1, 1, 1, 1, 0, None, None, None) == _cabi.ERR_ARG
     a = 4096  # fake, aligned, never dereferenced: validation fails first
     rc = lib.tdb_attn_fwd_fixed(a, a, a, a, 8, 8, 8, 8, 8, 8, 8, 8, 8, 8, 8, 8, None, None, 0, None, 0, None, None, 0, 0,
                                 None, 1, 16, 2, 32, 0.1, 0, 0, 0, None, a, None)

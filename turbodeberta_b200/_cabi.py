@@ -46,7 +46,7 @@ def _load() -> C.CDLL:
     lib.tdb_bucket_table.restype = i32
     lib.tdb_bucket_table.argtypes = [i32, i32, i32, vp, vp]
     lib.tdb_relpos_project.restype = i32
-    lib.tdb_relpos_project.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]
+    lib.tdb_relpos_project.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]
     lib.tdb_relpos_expand.restype = i32
     lib.tdb_relpos_expand.argtypes = [vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp]
     lib.tdb_attn_workspace_bytes.restype = sz

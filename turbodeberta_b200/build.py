@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtdb_b200.so")
-SOURCES = ["tdb_api.cu", "tables.cu", "attn_simt.cu", "attn_umma.cu"]
+SOURCES = ["tdb_api.cu", "tables.cu", "attn_simt.cu", "attn_umma.cu", "relpos_umma.cu"]
 HEADERS = ["tdb_internal.h", "ptx_sm100.cuh", os.path.join("..", "..", "include", "tdb_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

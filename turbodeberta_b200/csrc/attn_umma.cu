@@ -84,43 +84,42 @@ __device__ int g_timeline_n[3];
 #endif
 
 // ---------------------------------------------------------------------------------------------
-// Packed form: list of (sequence, first query row) per 128-row tile, built on the device from
-// cu_seqlens so that the host never reads lengths back.  Also validates cu_seqlens: a negative
-// length or an offset outside [0, T] sets status[1] and the sequence is dropped.
+// Packed form: list of (sequence, first query row) per 128-row tile, built on the device from cu_seqlens so that
+// the host never reads lengths back.  Tiles are ordered by decreasing sequence length (a counting sort on the
+// number of key tiles), so the device-wide work counter hands out the expensive tiles first and the short ones
+// fill the tail.  Also validates cu_seqlens: a negative length or an offset outside [0, T] sets status[1] and
+// the sequence is dropped.
+constexpr int LIST_BUCKETS = 1024;
 __global__ void __launch_bounds__(1024) build_tile_list_kernel(const int32_t* __restrict__ cu, int n_seqs,
                                                                 int64_t total_tokens, int32_t* ws, int cap,
                                                                 int32_t* status) {
-  __shared__ int scan[1024];
-  __shared__ int running;
-  if (threadIdx.x == 0) running = 0;
-  __syncthreads();
+  __shared__ int hist[LIST_BUCKETS];       // tiles per bucket, then the write cursor of the bucket
   int2* entries = reinterpret_cast<int2*>(ws + 4);
-  for (int base = 0; base < n_seqs; base += 1024) {
-    int s = base + threadIdx.x;
-    int len = 0, nt = 0;
-    if (s < n_seqs) {
-      int a = cu[s], b = cu[s + 1];
-      if (a < 0 || b < a || (int64_t)b > total_tokens) { atomicExch(status + 1, 1); }
-      else { len = b - a; nt = (len + BQ - 1) / BQ; }
-    }
-    scan[threadIdx.x] = nt;
-    __syncthreads();
-    for (int off = 1; off < 1024; off <<= 1) {
-      int v = threadIdx.x >= off ? scan[threadIdx.x - off] : 0;
-      __syncthreads();
-      scan[threadIdx.x] += v;
-      __syncthreads();
-    }
-    int start = running + scan[threadIdx.x] - nt;
+  for (int i = threadIdx.x; i < LIST_BUCKETS; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  auto tiles_of = [&](int s) {
+    const int a = cu[s], b = cu[s + 1];
+    if (a < 0 || b < a || (int64_t)b > total_tokens) { atomicExch(status + 1, 1); return 0; }
+    return (b - a + BQ - 1) / BQ;
+  };
+  for (int s = threadIdx.x; s < n_seqs; s += blockDim.x) {
+    const int nt = tiles_of(s);
+    if (nt > 0) atomicAdd(&hist[nt < LIST_BUCKETS ? nt : LIST_BUCKETS - 1], nt);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {                  // exclusive scan from the largest bucket down
+    int run = 0;
+    for (int bkt = LIST_BUCKETS - 1; bkt >= 0; --bkt) { const int c = hist[bkt]; hist[bkt] = run; run += c; }
+    ws[0] = run < cap ? run : cap;
+    if (cu[n_seqs] != (int32_t)total_tokens) atomicExch(status + 1, 1);
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s < n_seqs; s += blockDim.x) {
+    const int nt = tiles_of(s);
+    if (nt <= 0) continue;
+    const int start = atomicAdd(&hist[nt < LIST_BUCKETS ? nt : LIST_BUCKETS - 1], nt);
     for (int t = 0; t < nt; ++t)
       if (start + t < cap) entries[start + t] = make_int2(s, t * BQ);
-    __syncthreads();
-    if (threadIdx.x == 1023) running += scan[1023];
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) {
-    if (cu[n_seqs] != (int32_t)total_tokens) atomicExch(status + 1, 1);
-    ws[0] = running < cap ? running : cap;
   }
 }
 

@@ -116,10 +116,15 @@ TDB_API int tdb_bucket_table(int position_buckets, int max_relative_positions, i
 }
 
 TDB_API int tdb_relpos_project(const void* rel, const void* W, const void* bias, int two_span, int hidden, int H, int D,
-                       int dtype, void* out, void* stream) {
+                       int dtype, void* out, int32_t* status, void* stream) {
   if (!rel || !W || !out) { set_error("rel, W or out is null"); return TDB_ERR_ARG; }
   if (dtype != TDB_DTYPE_F32 && dtype != TDB_DTYPE_BF16) { set_error("dtype %d is not f32 or bf16", dtype); return TDB_ERR_DTYPE; }
   if (two_span <= 0 || hidden <= 0 || H <= 0 || D <= 0) { set_error("non-positive size"); return TDB_ERR_ARG; }
+  if (relpos_umma_applicable(rel, W, out, hidden, D, dtype) && (!bias || (reinterpret_cast<uintptr_t>(bias) & 1u) == 0)) {
+    if (!status) { set_error("status word pointer is null (required for the bf16 tensor-core projection)"); return TDB_ERR_ARG; }
+    if (H > 65535) { set_error("more than 65535 heads"); return TDB_ERR_SHAPE; }
+    return launch_relpos_project_umma(rel, W, bias, two_span, hidden, H, out, status, (cudaStream_t)stream);
+  }
   return launch_relpos_project(rel, W, bias, two_span, hidden, H, D, dtype, out, (cudaStream_t)stream);
 }
 

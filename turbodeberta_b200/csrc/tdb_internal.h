@@ -41,6 +41,9 @@ int cuda_fail(cudaError_t e, const char* what);
 int launch_bucket_table(int buckets, int max_pos, int delta_max, int16_t* out, cudaStream_t s);
 int launch_relpos_project(const void* rel, const void* W, const void* bias, int two_span, int hidden,
                           int H, int D, int dtype, void* out, cudaStream_t s);
+bool relpos_umma_applicable(const void* rel, const void* W, const void* out, int hidden, int D, int dtype);
+int launch_relpos_project_umma(const void* rel, const void* W, const void* bias, int two_span, int hidden, int H,
+                               void* out, int32_t* status, cudaStream_t s);
 int launch_relpos_expand(const void* table, const int16_t* idx, int idx_delta_max, int H, int two_span, int D,
                          int dtype, int exp_delta_max, int exp_rows, void* out, cudaStream_t s);
 int launch_attn_simt(const AttnParams& p, int dtype, cudaStream_t s);

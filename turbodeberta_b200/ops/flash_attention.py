@@ -74,10 +74,11 @@ _PENDING_STATUS: collections.deque = collections.deque(maxlen=512)
 def check_pending_status() -> None:
     """Read (one synchronisation) the device status words of every call since the last check that was made
     with ``check_status=False`` and raise if any bounded device wait gave up or any ``cu_seqlens`` was malformed."""
-    if not _PENDING_STATUS:
-        return
-    pending = list(_PENDING_STATUS)
+    pending = list(_PENDING_STATUS) + list(_relpos.PENDING_STATUS)
     _PENDING_STATUS.clear()
+    _relpos.PENDING_STATUS.clear()
+    if not pending:
+        return
     by_dev = {}
     for st in pending:
         by_dev.setdefault(st.device, []).append(st)

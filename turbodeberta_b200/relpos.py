@@ -12,6 +12,7 @@ the result keyed on the weights' versions.
 """
 from __future__ import annotations
 
+import collections
 import math
 from dataclasses import dataclass
 
@@ -20,6 +21,7 @@ import torch
 from . import _cabi as cabi
 
 _IDX_CACHE: dict = {}
+PENDING_STATUS: collections.deque = collections.deque(maxlen=512)
 
 
 def att_span(position_buckets: int, max_relative_positions: int) -> int:
@@ -68,10 +70,12 @@ def project(rel: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, 
         raise ValueError("projection weight does not match the relative embeddings / head count")
     D = hd // num_heads
     out = torch.empty(num_heads, two_span, D, dtype=rel.dtype, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         cabi.check(cabi.lib.tdb_relpos_project(cabi.ptr(rel), cabi.ptr(weight), cabi.ptr(bias), two_span, hidden,
                                                num_heads, D, cabi.dtype_code(rel.dtype), cabi.ptr(out),
-                                               cabi.stream_ptr(dev)))
+                                               cabi.ptr(status), cabi.stream_ptr(dev)))
+    PENDING_STATUS.append(status)          # read by ops.flash_attention.check_pending_status (no sync here)
     return out
 
 
