@@ -30,7 +30,7 @@ METRIC = "disentangled_attn_algorithmic_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on the default workload,
 # from the ncu capture summarised in profiles/attn_umma_config2.md.
-NCU_TRAFFIC_BYTES = 59.94e6     # profiles/attn_umma_config2.md: 56.31 MB read + 3.63 MB written
+NCU_TRAFFIC_BYTES = 60.93e6     # profiles/attn_umma_config2.md: 56.31 MB read + 4.62 MB written
 
 
 def parse():
@@ -39,7 +39,10 @@ def parse():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5f", "c5v", "c2full"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5f", "c5v", "c2full", "encoder"])
+    ap.add_argument("--encoder-batch", type=int, default=256, help="global batch of the encoder workload")
+    ap.add_argument("--encoder-layers", type=int, default=24)
+    ap.add_argument("--with-eager", action="store_true", help="encoder workload: also time the unpatched eager model on the GPU")
     ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "umma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -158,7 +161,8 @@ def run_reference(args):
     import numpy as np
     import torch
     from oracle import hf_eager
-    w = make_workload(args.workload, 0)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))      # torchrun exports OMP_NUM_THREADS=1; use every host core
+    w = make_workload(args.workload if args.workload != "encoder" else "c2", 0)
     n_sample = min(2, len(w.lengths))
     sample, desc = _cpu_sample(w, n_sample)
     threads = torch.get_num_threads()
@@ -201,6 +205,7 @@ def cpu_baseline(w, budget_s=12.0):
     import torch
     from oracle import hf_eager
     sample, desc = _cpu_sample(w, min(2, len(w.lengths)))
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     try:
         full, proj = _eager_step_fns(sample)
         full(); proj()
@@ -393,9 +398,112 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------- encoder workload
+def run_encoder(args):
+    """DeBERTa-v3-large encoder forward with the patched attention (configuration 4): batch 256 x seq 512, bf16,
+    random init, all-ones mask.  The batch is cut into contiguous slices, one per rank (strong scaling); every rank
+    runs its slice and the final hidden states are gathered over NCCL.  Metric: sequences per second."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from transformers import DebertaV2Config
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DebertaV2Model
+    from turbodeberta_b200 import sharding
+    from turbodeberta_b200.model import FlashDebertaV2Model
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = DebertaV2Config(vocab_size=128100, hidden_size=1024, num_hidden_layers=args.encoder_layers,
+                          num_attention_heads=16, intermediate_size=4096, hidden_act="gelu", relative_attention=True,
+                          position_buckets=256, max_relative_positions=-1, max_position_embeddings=512,
+                          norm_rel_ebd="layer_norm", share_att_key=True, pos_att_type=["p2c", "c2p"],
+                          position_biased_input=False, type_vocab_size=0)
+    torch.manual_seed(1004)
+    model = FlashDebertaV2Model(cfg).eval().to(dev, torch.bfloat16)
+    B, L = args.encoder_batch, 512
+    gen = torch.Generator().manual_seed(1004)
+    ids_all = torch.randint(0, 128100, (B, L), generator=gen)
+    sl = sharding.shard_batch(B, world, rank)
+    ids = ids_all[sl].pin_memory()
+    mask = torch.ones(ids.shape, dtype=torch.long, device=dev)
+
+    @torch.no_grad()
+    def step(model=model):
+        x = ids.to(dev, non_blocking=True)
+        h = model(input_ids=x, attention_mask=mask).last_hidden_state
+        if world > 1:
+            h = sharding.gather_padded(h, B)
+        return h
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        out = step()
+    barrier()
+    assert torch.isfinite(out.float()).all()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start(); time.sleep(1.5)
+    barrier()
+    w0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step()
+    e1.record()
+    barrier()
+    w1 = time.time()
+    ms = e0.elapsed_time(e1) / args.steps
+    checksum = float(out.float().abs().mean())          # device -> host read of the result
+    clocks = sampler.stop(w0, w1) if sampler else None
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    eager = None
+    if args.with_eager and rank == 0:
+        hf = DebertaV2Model(cfg).eval().to(dev, torch.bfloat16)
+        hf.load_state_dict(model.state_dict())
+        n = min(ids.shape[0], 64)
+        with torch.no_grad():
+            for _ in range(2):
+                hf(input_ids=ids[:n].to(dev), attention_mask=mask[:n])
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(3):
+                hf(input_ids=ids[:n].to(dev), attention_mask=mask[:n])
+            torch.cuda.synchronize()
+            eager = {"seq_per_s": n / ((time.perf_counter() - t0) / 3), "batch": n,
+                     "what": "unpatched transformers DebertaV2Model (eager attention), bf16, same GPU"}
+        del hf
+    if rank == 0:
+        line = {"metric": "deberta_v3_large_encoder_seq_per_s", "value": B / (ms * 1e-3), "unit": "seq/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"c4_v3large_{args.encoder_layers}layers_b{B}_l512_allones", "global_batch": B,
+                           "seq_len": L, "parallelism": f"batch shards x{world}, NCCL all-gather of outputs",
+                           "l2": "activations of one step (hundreds of MB) exceed L2"},
+                "e2e": {"value": B / (ms * 1e-3), "unit": "seq/s", "h2d_bytes_per_step": int(ids.numel() * 8),
+                        "d2h_bytes_per_step": 4, "note": "token ids copied from pinned host memory every step"},
+                "output_abs_mean": checksum, "clocks": clocks, "eager_gpu": eager}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "encoder":
+        run_encoder(a)
     else:
         run_ours(a)

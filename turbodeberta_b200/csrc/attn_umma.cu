@@ -44,8 +44,8 @@ constexpr int NCT = NCW * 32;                   // CUDA-core threads
 constexpr int NTHREADS = (NCW + 3) * 32;       // + TMA producer warp, MMA warp, scheduler warp
 constexpr int STG_STRIDE = 336;                 // bytes per staging row: 160 bf16 + 16 pad (odd multiple of 16)
 constexpr int STG_COLS = 160;
-constexpr uint32_t OFF_Q = 0, OFF_K = 16384, OFF_V = 32768, OFF_KR = 49152, OFF_QR = 81920;
-constexpr uint32_t OFF_STC = 114688, OFF_STP = OFF_STC + BQ * STG_STRIDE, OFF_XCH = OFF_STP + BK * STG_STRIDE;
+constexpr uint32_t OFF_Q = 0 /* two buffers */, OFF_K = 32768, OFF_V = 49152, OFF_KR = 65536, OFF_QR = 98304;
+constexpr uint32_t OFF_STC = 131072, OFF_STP = OFF_STC + BQ * STG_STRIDE, OFF_XCH = OFF_STP + BK * STG_STRIDE;
 constexpr uint32_t OFF_BAR = OFF_XCH + GROUPS * BQ * 4;
 constexpr uint32_t OFF_WORK = OFF_BAR + 256;        // ring of work items published by the scheduler lane
 constexpr uint32_t OFF_CUR = OFF_WORK + 256;        // the CUDA-core warps' agreed copy of their current item
@@ -56,9 +56,9 @@ static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 constexpr uint32_t TM_S = 0, TM_O = 128, TM_RING = 192, TM_P = 448, TM_COLS = 512;
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per wait, then give up
 
-enum Bar { Q_FULL = 0, K_FULL, K_EMPTY, V_FULL, V_EMPTY, KR_FULL, KR_EMPTY, QR_FULL, QR_EMPTY,
+enum Bar { Q_FULL = 0 /* Q_FULL + buffer */, Q_FULL1, Q_EMPTY /* Q_EMPTY + buffer */, Q_EMPTY1, K_FULL, K_EMPTY, V_FULL, V_EMPTY, KR_FULL, KR_EMPTY, QR_FULL, QR_EMPTY,
            S_FULL, S_TAKEN, RING_FULL_A, RING_FULL_B, RING_FREE_A, RING_FREE_B, P_READY, O_FULL,
-           Q_EMPTY, O_TAKEN, DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
+           O_TAKEN, DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
            WORK_EMPTY0, WORK_EMPTY1, WORK_EMPTY2, WORK_EMPTY3, NBARS };
 constexpr int WORK_RING = 4;
 constexpr int WORK_READERS = 3 + 1 + NCW;       // three producer lanes, the MMA lane, one lane per CUDA-core warp
@@ -218,8 +218,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   const uint32_t sQ = sbase + OFF_Q, sK = sbase + OFF_K, sV = sbase + OFF_V, sKr = sbase + OFF_KR, sQr = sbase + OFF_QR;
   const uint32_t stC = sbase + OFF_STC, stP = sbase + OFF_STP, sX = sbase + OFF_XCH;
   const uint32_t bars = sbase + OFF_BAR;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_BAR + 232);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_BAR + 240);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_CUR + 48);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_CUR + 56);
   Work* work_ring = reinterpret_cast<Work*>(gbase + OFF_WORK);
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
   auto wait = [&](int i, uint32_t parity) { return mbar_wait(bar(i), parity, abort_flag, p.status, 1 + i, WAIT_LIMIT_NS); };
@@ -309,17 +309,17 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         ++n;
       }
       release(n);
-    } else if (lane == 2) {                // Q, once per work item
+    } else if (lane == 2) {                // Q, once per work item, into alternating buffers
       Work k;
-      int n = 0, m = 0;                    // m counts items with tensor work
+      int n = 0;
       while (next_tensor_item(n, k)) {
-        if (m > 0) wait(Q_EMPTY, (uint32_t)((m - 1) & 1));
+        const int b = n & 1;
+        if (n >= 2) wait(Q_EMPTY + b, (uint32_t)(((n >> 1) - 1) & 1));
         if (!*abort_flag) {
-          mbar_expect_tx(bar(Q_FULL), BQ * HD * 2);
-          tma_load_4d(sQ, &tm_q, bar(Q_FULL), 0, (int)(k.tok0 + k.q0), k.h, k.bcoord);
+          mbar_expect_tx(bar(Q_FULL + b), BQ * HD * 2);
+          tma_load_4d(sQ + (uint32_t)b * (BQ * HD * 2), &tm_q, bar(Q_FULL + b), 0, (int)(k.tok0 + k.q0), k.h, k.bcoord);
         }
-        TDB_TL(2, 900 + m);
-        ++m;
+        TDB_TL(2, 900 + n);
         release(n);
         ++n;
       }
@@ -370,86 +370,105 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       const uint32_t tRing[2] = {tmem + TM_RING, tmem + TM_RING + HALF};
       int fills[2] = {0, 0};               // how often each ring slot has been filled so far
 
-      // The three products of key tile g (global count) that do not depend on the softmax of an earlier tile.
-      auto issue_scores = [&](int g) {
-        const uint32_t ph = (uint32_t)(g & 1);
-        if (C2P) {                         // content->position band: one 256-column product into both slots
-          wait(KR_FULL, ph);
-          if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
-          if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
-          tc_fence_after();
+      // A position in this CTA's stream of key tiles: ring index of the work item, key tile inside it.
+      struct TileCur { int n, it; bool ok; Work k; };
+      auto cur_next = [&](TileCur& c) {
+        if (c.it + 1 < c.k.n_kv) { ++c.it; return; }
+        ++c.n; c.it = 0;
+        c.ok = fetch(c.n, c.k);
+      };
+      auto wait_q = [&](const TileCur& c) {                 // the item's Q tile has landed (once per item)
+        if (c.it == 0) wait(Q_FULL + (c.n & 1), (uint32_t)((c.n >> 1) & 1));
+      };
+      auto wait_ring_free = [&]() {
+        if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
+        if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
+      };
+      auto ring_filled = [&]() {
+        tc_commit(bar(RING_FULL_A));
+        tc_commit(bar(RING_FULL_B));
+        ++fills[0]; ++fills[1];
+      };
+      // content->position band of key tile g (global count): one 256-column product into the band buffer
+      auto issue_c = [&](const TileCur& c, int g) {
+        wait(KR_FULL, (uint32_t)(g & 1));
+        wait_q(c);
+        wait_ring_free();
+        tc_fence_after();
+        const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQ + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
-          tc_commit(bar(RING_FULL_A));
-          tc_commit(bar(RING_FULL_B));
-          tc_commit(bar(KR_EMPTY));
-          ++fills[0]; ++fills[1];
-          TDB_TL(1, 1000 + g);
-        }
-        wait(K_FULL, ph);                  // content score
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQc + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
+        ring_filled();
+        tc_commit(bar(KR_EMPTY));
+        TDB_TL(1, 1000 + g);
+      };
+      // content score of key tile g; the last one of an item releases the item's Q buffer
+      auto issue_s = [&](const TileCur& c, int g) {
+        wait(K_FULL, (uint32_t)(g & 1));
+        if (!C2P) wait_q(c);
         if (g > 0) wait(S_TAKEN, (uint32_t)((g - 1) & 1));
         tc_fence_after();
+        const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQ + 2 * k, dK + 2 * k, ID_S, k > 0);
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQc + 2 * k, dK + 2 * k, ID_S, k > 0);
         tc_commit(bar(S_FULL));
+        if (c.it + 1 == c.k.n_kv) tc_commit(bar(Q_EMPTY + (c.n & 1)));
         TDB_TL(1, 2000 + g);
-        if (P2C) {                         // position->content band (rows = keys), once the c2p band has been drained
-          wait(QR_FULL, ph);
-          if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
-          if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
+      };
+      // position->content band of key tile g (rows = keys), once the c2p band has been drained; releases K
+      auto issue_p2 = [&](int g) {
+        if (P2C) {
+          wait(QR_FULL, (uint32_t)(g & 1));
+          wait_ring_free();
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dK + 2 * k, dQr + 2 * k, ID_BAND, k > 0);
-          tc_commit(bar(RING_FULL_A));
-          tc_commit(bar(RING_FULL_B));
+          ring_filled();
           tc_commit(bar(QR_EMPTY));
-          ++fills[0]; ++fills[1];
         }
         tc_commit(bar(K_EMPTY));
         TDB_TL(1, 3000 + g);
       };
-
-      Work cur, nx;
-      int n = 0, g = 0, n_item = 0, it = 0;
-      if (next_tensor_item(n, cur)) {
-        wait(Q_FULL, 0);
-        issue_scores(0);
-        if (cur.n_kv == 1) tc_commit(bar(Q_EMPTY));
-        while (true) {
-          // look ahead: the key tile after (cur, it), possibly the first one of the next work item
-          bool has_next = true, new_item = false;
-          int n_next = n;
-          if (it + 1 >= cur.n_kv) {
-            new_item = true;
-            n_next = n + 1;
-            has_next = next_tensor_item(n_next, nx);
-          }
-          if (has_next) {
-            if (new_item) wait(Q_FULL, (uint32_t)((n_item + 1) & 1));
-            issue_scores(g + 1);           // runs while the CUDA warps work on key tile g
-            const bool last_of_item = new_item ? (nx.n_kv == 1) : (it + 2 == cur.n_kv);
-            if (last_of_item) tc_commit(bar(Q_EMPTY));
-          }
-          wait(V_FULL, (uint32_t)(g & 1));
-          wait(P_READY, (uint32_t)(g & 1));
-          if (it == 0 && n_item > 0) wait(O_TAKEN, (uint32_t)((n_item - 1) & 1));
-          tc_fence_after();
+      // O += P . V of key tile g; the first one of an item overwrites O, so the previous item must have read it
+      auto issue_pv = [&](const TileCur& c, int g, int item_ordinal) {
+        wait(V_FULL, (uint32_t)(g & 1));
+        wait(P_READY, (uint32_t)(g & 1));
+        if (c.it == 0 && item_ordinal > 0) wait(O_TAKEN, (uint32_t)((item_ordinal - 1) & 1));
+        tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            mma_ts(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (it > 0 || k > 0) ? 1u : 0u);
-          tc_commit(bar(O_FULL));
-          tc_commit(bar(V_EMPTY));
-          TDB_TL(1, 4000 + g);
-          if (new_item) {                  // done with the current item (and with the end marker, if that is what follows)
-            release(n);
-            n = n_next;
+        for (int k = 0; k < BK / 16; ++k)
+          mma_ts(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (c.it > 0 || k > 0) ? 1u : 0u);
+        tc_commit(bar(O_FULL));
+        tc_commit(bar(V_EMPTY));
+        TDB_TL(1, 4000 + g);
+      };
+
+      // Issue order: C(0) S(0) P2(0) C(1) | S(1) P2(1) C(2) PV(0) | S(2) P2(2) C(3) PV(1) | ...  so that the band of
+      // tile g+2 is under way as soon as the band buffer has been drained of tile g+1, well before the CUDA warps
+      // ask for it, and P.V of tile g never delays the scores of the tiles after it.
+      TileCur cc, cs, cv;                  // c2p stream (two tiles ahead), score/p2c stream (one ahead), P.V stream
+      cc.n = 0; cc.it = 0; cc.ok = fetch(0, cc.k);
+      cs = cc; cv = cc;
+      int gc = 0, gs = 0, gv = 0, items_done = 0;
+      if (cv.ok) {
+        if (C2P) { issue_c(cc, gc++); cur_next(cc); }
+        issue_s(cs, gs); issue_p2(gs); ++gs;
+        if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
+        while (true) {
+          TileCur nx = cs;
+          cur_next(nx);
+          if (nx.ok) {
+            cs = nx;
+            issue_s(cs, gs); issue_p2(gs); ++gs;
+            if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
           }
-          if (!has_next) break;
-          ++g;
-          if (new_item) { cur = nx; it = 0; ++n_item; } else { ++it; }
+          issue_pv(cv, gv++, items_done);
+          if (cv.it + 1 == cv.k.n_kv) { release(cv.n); ++items_done; }
+          cur_next(cv);
+          if (!cv.ok) break;
         }
       }
-      release(n);                          // the end-of-stream marker
+      release(cv.n);                       // the end-of-stream marker
       // Everything issued above must have retired before tensor memory is released.
       tc_commit(bar(DONE));
       int never = 0;                       // this wait runs even after an abort, with its own limit
@@ -598,11 +617,15 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             pk[e / 2] = pack_bf16x2(a, b);
           }
         }
-        // row maximum over the four threads of the row
+        // The barrier below closes the reads of the p2c staging rows of this key tile (so the next tile's band can
+        // be drained into them right away, which frees tensor memory for the MMA warp early) and publishes the
+        // per-thread maxima for the row maximum over the four threads of a row.
         TL0(12000 + g);
         sts_f32(x_mine, mx);
-        bar_quadrant(qd);
+        bar_all_cuda_warps();
         TL0(13000 + g);
+        if (has_next) drain_p2();
+        TL0(13500 + g);
 #pragma unroll
         for (int gg = 0; gg < GROUPS; ++gg) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t)));
         const float row_max = mx * sl2;                                // sl2 > 0
@@ -641,11 +664,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_READY));
         TL0(15000 + g);
-        bar_all_cuda_warps();                                          // p2c staging rows and the exchange buffer are free again
-        TL0(16000 + g);
-        if (has_next) drain_p2();
-        TL0(17000 + g);
-        bar_all_cuda_warps();                                          // staging of the next key tile is complete
+        bar_all_cuda_warps();                                          // next tile's staging complete; exchange buffer free
         TL0(18000 + g);
       }
       // ---- epilogue of the work item: O / l -> global ----
