@@ -37,8 +37,13 @@ using namespace ptx;
 namespace {
 
 constexpr int BQ = 128, BK = 128, HD = 64, BAND = 256, HALF = 128;
-constexpr int GROUPS = 4;                       // threads per query row
-constexpr int KPT = BK / GROUPS;                // keys per thread in the softmax (32)
+#ifndef TDB_GROUPS
+#define TDB_GROUPS 4
+#endif
+constexpr int GROUPS = TDB_GROUPS;              // threads per query row (2 or 4)
+static_assert(GROUPS == 2 || GROUPS == 4, "two or four threads per query row");
+constexpr int KPT = BK / GROUPS;                // keys per thread in the softmax
+constexpr int OPT = HD / GROUPS;                // output columns per thread
 constexpr int NCW = 4 * GROUPS;                 // CUDA-core warps
 constexpr int NCT = NCW * 32;                   // CUDA-core threads
 constexpr int NTHREADS = (NCW + 3) * 32;       // + TMA producer warp, MMA warp, scheduler warp
@@ -146,6 +151,24 @@ __device__ __forceinline__ void sts_128(uint32_t addr, uint32_t a, uint32_t b, u
 }
 __device__ __forceinline__ void bar_all_cuda_warps() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 __device__ __forceinline__ void bar_quadrant(int qd) { asm volatile("bar.sync %0, %1;" ::"r"(2 + qd), "n"(GROUPS * 32) : "memory"); }
+
+// N consecutive 32-bit columns of this thread's tensor-memory lane (N = 16, 32 or 64).
+template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  if constexpr (N == 16) { tmem_ld16(taddr, r); tmem_ld_wait16(r); }
+  else {
+#pragma unroll
+    for (int c = 0; c < N / 32; ++c) tmem_ld32(taddr + 32 * c, r + 32 * c);
+#pragma unroll
+    for (int c = 0; c < N / 32; ++c) tmem_ld_wait32(r + 32 * c);
+  }
+}
+template <int N> __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
+  if constexpr (N == 16) { tmem_st16(taddr, r); }
+  else {
+#pragma unroll
+    for (int c = 0; c < N / 32; ++c) tmem_st32(taddr + 32 * c, r + 32 * c);
+  }
+}
 
 // Move 32 fp32 columns of this thread's tensor-memory lane to 32 bf16 of a staging row.
 __device__ __forceinline__ void drain_chunk(uint32_t taddr, uint32_t dst_saddr) {
@@ -480,15 +503,15 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     const int row_t = qd * 32 + lane;                                  // tensor-memory lane = query row (or key row of P2)
     const uint32_t lane_base = ((uint32_t)(qd * 32)) << 16;
     const uint32_t tS = tmem + lane_base + TM_S + KPT * grp;
-    const uint32_t tO = tmem + lane_base + TM_O + (HD / GROUPS) * grp;
+    const uint32_t tO = tmem + lane_base + TM_O + OPT * grp;
     const uint32_t tP = tmem + lane_base + TM_P + (KPT / 2) * grp;
-    const uint32_t tRingMine = tmem + lane_base + TM_RING + 32 * grp;  // + HALF for slot B
+    const uint32_t tRingMine = tmem + lane_base + TM_RING + (HALF / GROUPS) * grp;  // + HALF for slot B
     const float sl2 = p.sm_scale * 1.4426950408889634f;
     // staging rows: c2p row i holds band columns [32*qd, +160); p2c row j holds band columns [96 - 32*(j/32), +160)
     const uint32_t c_row = stC + (uint32_t)row_t * STG_STRIDE;
     const uint32_t p_row = stP + (uint32_t)row_t * STG_STRIDE;
     const uint32_t c_read = c_row + 2u * (uint32_t)(lane + (BK - 1) - KPT * grp);          // key e of this thread: c_read - 2e
-    const uint32_t p_read = stP + (uint32_t)(KPT * grp) * STG_STRIDE + 2u * (uint32_t)(row_t + 31);  // + e*STRIDE - 2e
+    const uint32_t p_read = stP + (uint32_t)(KPT * grp) * STG_STRIDE + 2u * (uint32_t)(row_t + 31);  // + e*STRIDE - 2*(e%32)
     const uint32_t x_mine = sX + 4u * (uint32_t)(grp * BQ + row_t);
     int drains[2] = {0, 0};
 
@@ -497,10 +520,13 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       wait(half ? RING_FULL_B : RING_FULL_A, (uint32_t)(drains[half] & 1));
       ++drains[half];
       tc_fence_after();
-      const int col = HALF * half + 32 * grp;                          // band column of this thread's chunk
-      const int local = col - (kind == 0 ? 32 * qd : 96 - 32 * qd);    // position inside the staging row
-      if (local >= 0 && local + 32 <= STG_COLS)
-        drain_chunk(tRingMine + (uint32_t)(HALF * half), (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local);
+#pragma unroll
+      for (int c = 0; c < HALF / GROUPS / 32; ++c) {
+        const int col = HALF * half + (HALF / GROUPS) * grp + 32 * c;  // band column of this 32-column chunk
+        const int local = col - (kind == 0 ? 32 * qd : 96 - 32 * qd);  // position inside the staging row
+        if (local >= 0 && local + 32 <= STG_COLS)
+          drain_chunk(tRingMine + (uint32_t)(HALF * half + 32 * c), (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(half ? RING_FREE_B : RING_FREE_A));
@@ -550,9 +576,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_fence_after();
         float s[KPT];
         {
-          uint32_t* sr = reinterpret_cast<uint32_t*>(s);
-          tmem_ld32(tS, sr);
-          tmem_ld_wait32(sr);
+          tmem_ld_cols<KPT>(tS, reinterpret_cast<uint32_t*>(s));
         }
         tc_fence_before();
         __syncwarp();
@@ -591,8 +615,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           for (int e = 0; e < KPT; e += 2) {
             float x0 = s[e], x1 = s[e + 1];
             if (P2C) {
-              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
-              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
+              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * (e & 31)));
+              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31)));
             }
             s[e] = x0; s[e + 1] = x1;
             mx = fmaxf(mx, fmaxf(x0, x1));
@@ -605,8 +629,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           for (int e = 0; e < KPT; e += 2) {
             float x0 = s[e], x1 = s[e + 1];
             if (P2C) {
-              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * e));
-              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * (e + 1)));
+              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * (e & 31)));
+              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31)));
             }
             x0 = (e < nvalid) ? x0 : -CUDART_INF_F;
             x1 = (e + 1 < nvalid) ? x1 : -CUDART_INF_F;
@@ -647,18 +671,17 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           wait(O_FULL, (uint32_t)((g - 1) & 1));
           tc_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
-            uint32_t r[16];
-            tmem_ld16(tO, r);
-            tmem_ld_wait16(r);
+            uint32_t r[OPT];
+            tmem_ld_cols<OPT>(tO, r);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-            tmem_st16(tO, r);
+            for (int e = 0; e < OPT; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st_cols<OPT>(tO, r);
           }
         }
         TL0(14000 + g);
         l_part = (it > 0 ? l_part * alpha : 0.f) + lsum;
         m_run = m_new;
-        tmem_st16(tP, pk);
+        tmem_st_cols<KPT / 2>(tP, pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -676,9 +699,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       wait(O_FULL, (uint32_t)((g - 1) & 1));
       TL0(20000 + n_item);
       tc_fence_after();
-      uint32_t r[16];
-      tmem_ld16(tO, r);
-      tmem_ld_wait16(r);
+      uint32_t r[OPT];
+      tmem_ld_cols<OPT>(tO, r);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(O_TAKEN));                        // the next item's first P.V may overwrite O
@@ -686,15 +708,16 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       const float inv = 1.f / l_tot;
       if (row < cur.rows) {
         const bool valid = row < cur.len;
-        uint32_t outw[8];
+        uint32_t outw[OPT / 2];
 #pragma unroll
-        for (int e = 0; e < 16; e += 2)
+        for (int e = 0; e < OPT; e += 2)
           outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)cur.bcoord * p.o_sb +
-                              (cur.tok0 + row) * p.o_st + (int64_t)cur.h * p.o_sh + (HD / GROUPS) * grp;
+                              (cur.tok0 + row) * p.o_st + (int64_t)cur.h * p.o_sh + OPT * grp;
         uint4* dst = reinterpret_cast<uint4*>(orow);
-        dst[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-        dst[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+#pragma unroll
+        for (int i = 0; i < OPT / 8; ++i)
+          dst[i] = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
         if (p.lse && grp == 0)
           p.lse[(int64_t)cur.bcoord * p.lse_sb + (int64_t)cur.h * p.lse_sh + cur.tok0 + row] =
               valid ? (m_run * 0.6931471805599453f + logf(l_tot)) : 0.f;
