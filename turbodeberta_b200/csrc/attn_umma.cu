@@ -186,6 +186,16 @@ __device__ __forceinline__ void drain_chunk(uint32_t taddr, uint32_t dst_saddr) 
 }
 
 // One unit of work: a 128-query tile of one sequence for one head.
+// A 128x128 score tile whose distances q - k all lie at or beyond the saturation distance (on one side): every
+// score of the tile uses the same table row, so c2p is one value per query row and p2c one value per key, and the
+// position bands shrink from 256 columns to the 16-column minimum of the MMA.
+__device__ __forceinline__ bool tile_saturated(const AttnParams& p, int q0, int k0) {
+  const int sat = p.exp_delta_max - TDB_EXPAND_MARGIN;
+  const int d = q0 - k0;
+  return (d - (BK - 1) >= sat) || (d + (BQ - 1) <= -sat);
+}
+constexpr int SATN = 16;
+
 struct Work {
   int q0, len, rows, bcoord, h, n_kv;      // n_kv == 0: tile of padded query rows only (zeros, no tensor work)
   int64_t tok0;
@@ -212,11 +222,13 @@ __device__ __forceinline__ bool get_work(const AttnParams& p, int total_tiles, i
   return true;
 }
 
-template <bool C2P, bool P2C>
+// LONG: sequences can be long enough for saturated tiles (compiled out otherwise, which keeps the common kernel lean).
+template <bool C2P, bool P2C, bool LONG>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kr,
-                 const __grid_constant__ CUtensorMap tm_qr) {
+                 const __grid_constant__ CUtensorMap tm_qr, const __grid_constant__ CUtensorMap tm_kr16,
+                 const __grid_constant__ CUtensorMap tm_qr16) {
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -258,8 +270,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   }
   if (warp == NCW && lane == 0) {
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
-    if (C2P) prefetch_tmap(&tm_kr);
-    if (P2C) prefetch_tmap(&tm_qr);
+    if (C2P) { prefetch_tmap(&tm_kr); prefetch_tmap(&tm_kr16); }
+    if (P2C) { prefetch_tmap(&tm_qr); prefetch_tmap(&tm_qr16); }
   }
   if (warp == NCW + 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TM_COLS);
@@ -292,11 +304,12 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           const uint32_t pe = (uint32_t)((g - 1) & 1);
           int x0 = k.q0 - k0 - (BK - 1) + p.exp_delta_max;
           x0 = x0 < 0 ? 0 : (x0 > p.exp_rows - BAND ? p.exp_rows - BAND : x0);
+          const bool sat = LONG && tile_saturated(p, k.q0, k0);
           if (C2P) {
             if (g > 0) wait(KR_EMPTY, pe);
             if (!*abort_flag) {
-              mbar_expect_tx(bar(KR_FULL), BAND * HD * 2);
-              tma_load_3d(sKr, &tm_kr, bar(KR_FULL), 0, x0, k.h);
+              mbar_expect_tx(bar(KR_FULL), (sat ? SATN : BAND) * HD * 2);
+              tma_load_3d(sKr, sat ? &tm_kr16 : &tm_kr, bar(KR_FULL), 0, x0, k.h);
             }
           }
           if (g > 0) wait(K_EMPTY, pe);
@@ -307,8 +320,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           if (P2C) {
             if (g > 0) wait(QR_EMPTY, pe);
             if (!*abort_flag) {
-              mbar_expect_tx(bar(QR_FULL), BAND * HD * 2);
-              tma_load_3d(sQr, &tm_qr, bar(QR_FULL), 0, x0, k.h);
+              mbar_expect_tx(bar(QR_FULL), (sat ? SATN : BAND) * HD * 2);
+              tma_load_3d(sQr, sat ? &tm_qr16 : &tm_qr, bar(QR_FULL), 0, x0, k.h);
             }
           }
           TDB_TL(2, 100 + g);
@@ -386,6 +399,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     if (lane == 0) {
       constexpr uint32_t ID_S = make_idesc_bf16(128, BK, 0);
       constexpr uint32_t ID_BAND = make_idesc_bf16(128, BAND, 0);
+      constexpr uint32_t ID_SAT = make_idesc_bf16(128, SATN, 0);
       constexpr uint32_t ID_PV = make_idesc_bf16(128, HD, 1);
       const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
       const uint64_t dKr = smem_desc_sw128(sKr), dQr = smem_desc_sw128(sQr);
@@ -394,11 +408,16 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       int fills[2] = {0, 0};               // how often each ring slot has been filled so far
 
       // A position in this CTA's stream of key tiles: ring index of the work item, key tile inside it.
-      struct TileCur { int n, it; bool ok; Work k; };
+      struct TileCur { int n, it, n_kv, q0; bool ok; };
+      auto cur_fetch = [&](TileCur& c) {
+        Work k;
+        c.ok = fetch(c.n, k);
+        c.n_kv = k.n_kv; c.q0 = k.q0;
+      };
       auto cur_next = [&](TileCur& c) {
-        if (c.it + 1 < c.k.n_kv) { ++c.it; return; }
+        if (c.it + 1 < c.n_kv) { ++c.it; return; }
         ++c.n; c.it = 0;
-        c.ok = fetch(c.n, c.k);
+        cur_fetch(c);
       };
       auto wait_q = [&](const TileCur& c) {                 // the item's Q tile has landed (once per item)
         if (c.it == 0) wait(Q_FULL + (c.n & 1), (uint32_t)((c.n >> 1) & 1));
@@ -419,8 +438,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         wait_ring_free();
         tc_fence_after();
         const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
+        const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQc + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQc + 2 * k, dKr + 2 * k, idesc, k > 0);
         ring_filled();
         tc_commit(bar(KR_EMPTY));
         TDB_TL(1, 1000 + g);
@@ -435,17 +455,18 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQc + 2 * k, dK + 2 * k, ID_S, k > 0);
         tc_commit(bar(S_FULL));
-        if (c.it + 1 == c.k.n_kv) tc_commit(bar(Q_EMPTY + (c.n & 1)));
+        if (c.it + 1 == c.n_kv) tc_commit(bar(Q_EMPTY + (c.n & 1)));
         TDB_TL(1, 2000 + g);
       };
       // position->content band of key tile g (rows = keys), once the c2p band has been drained; releases K
-      auto issue_p2 = [&](int g) {
+      auto issue_p2 = [&](const TileCur& c, int g) {
         if (P2C) {
           wait(QR_FULL, (uint32_t)(g & 1));
           wait_ring_free();
           tc_fence_after();
+          const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dK + 2 * k, dQr + 2 * k, ID_BAND, k > 0);
+          for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dK + 2 * k, dQr + 2 * k, idesc, k > 0);
           ring_filled();
           tc_commit(bar(QR_EMPTY));
         }
@@ -470,23 +491,23 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       // tile g+2 is under way as soon as the band buffer has been drained of tile g+1, well before the CUDA warps
       // ask for it, and P.V of tile g never delays the scores of the tiles after it.
       TileCur cc, cs, cv;                  // c2p stream (two tiles ahead), score/p2c stream (one ahead), P.V stream
-      cc.n = 0; cc.it = 0; cc.ok = fetch(0, cc.k);
+      cc.n = 0; cc.it = 0; cur_fetch(cc);
       cs = cc; cv = cc;
       int gc = 0, gs = 0, gv = 0, items_done = 0;
       if (cv.ok) {
         if (C2P) { issue_c(cc, gc++); cur_next(cc); }
-        issue_s(cs, gs); issue_p2(gs); ++gs;
+        issue_s(cs, gs); issue_p2(cs, gs); ++gs;
         if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
         while (true) {
           TileCur nx = cs;
           cur_next(nx);
           if (nx.ok) {
             cs = nx;
-            issue_s(cs, gs); issue_p2(gs); ++gs;
+            issue_s(cs, gs); issue_p2(cs, gs); ++gs;
             if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
           }
           issue_pv(cv, gv++, items_done);
-          if (cv.it + 1 == cv.k.n_kv) { release(cv.n); ++items_done; }
+          if (cv.it + 1 == cv.n_kv) { release(cv.n); ++items_done; }
           cur_next(cv);
           if (!cv.ok) break;
         }
@@ -516,10 +537,17 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     int drains[2] = {0, 0};
 
     // Drain one band half from ring slot `half`.  kind 0: c2p (window starts at 32*qd), kind 1: p2c (96 - 32*qd).
-    auto drain_half = [&](int half, int kind) {
+    auto drain_half = [&](int half, int kind, bool sat) {
       wait(half ? RING_FULL_B : RING_FULL_A, (uint32_t)(drains[half] & 1));
       ++drains[half];
       tc_fence_after();
+      if (sat) {                                                       // one value per row: column 0 of the band
+        if (half == 0 && grp == 0) {
+          uint32_t r[16];
+          tmem_ld_cols<16>(tmem + lane_base + TM_RING, r);
+          sts_f32(kind == 0 ? c_row : stP + 4u * (uint32_t)row_t, __uint_as_float(r[0]));
+        }
+      } else
 #pragma unroll
       for (int c = 0; c < HALF / GROUPS / 32; ++c) {
         const int col = HALF * half + (HALF / GROUPS) * grp + 32 * c;  // band column of this 32-column chunk
@@ -531,12 +559,12 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(half ? RING_FREE_B : RING_FREE_A));
     };
-    auto drain_c = [&]() { if (C2P) { drain_half(0, 0); drain_half(1, 0); } };
-    auto drain_p2 = [&]() { if (P2C) { drain_half(0, 1); drain_half(1, 1); } };
+    auto drain_c = [&](bool sat) { if (C2P) { drain_half(0, 0, sat); drain_half(1, 0, sat); } };
+    auto drain_p2 = [&](bool sat) { if (P2C) { drain_half(0, 1, sat); drain_half(1, 1, sat); } };
 
 #define TL0(evt) do { if (tid == 0) TDB_TL(0, evt); } while (0)
     TL0(1);
-    struct CurItem { Work k; int has_next; };
+    struct CurItem { Work k; int next_q0; int has_next; };
     volatile CurItem* cur_shared = reinterpret_cast<volatile CurItem*>(gbase + OFF_CUR);
     Work cur;
     int g = 0, n_item = 0;
@@ -549,6 +577,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const bool more = k.n_kv > 0 && fetch(n + 1, nk);
         CurItem* c = const_cast<CurItem*>(cur_shared);
         c->k = k;
+        c->next_q0 = nk.q0;
         c->has_next = more ? 1 : 0;
       }
       bar_all_cuda_warps();
@@ -557,19 +586,24 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         cur = c->k;
       }
       const bool item_follows = cur_shared->has_next != 0;
+      const int next_q0 = cur_shared->next_q0;
       if (cur.n_kv <= 0) {
         if (lane == 0) release(n);
         break;
       }
       if (n == 0) {                                                    // bands of the very first key tile
-        drain_c();
-        drain_p2();
+        const bool sat0 = LONG && tile_saturated(p, cur.q0, 0);
+        drain_c(sat0);
+        drain_p2(sat0);
         bar_all_cuda_warps();
       }
       float m_run = 0.f, l_part = 0.f;
       for (int it = 0; it < cur.n_kv; ++it, ++g) {
         const bool has_next = (it + 1 < cur.n_kv) || item_follows;
         const int nvalid = cur.len - it * BK - KPT * grp;            // keys e >= nvalid of this thread are masked
+        const bool sat = LONG && tile_saturated(p, cur.q0, it * BK);   // this key tile, and the one after it
+        const bool sat_n = LONG && ((it + 1 < cur.n_kv) ? tile_saturated(p, cur.q0, (it + 1) * BK)
+                                                        : tile_saturated(p, next_q0, 0));
         TL0(10000 + g);
         wait(S_FULL, (uint32_t)(g & 1));
         TL0(11000 + g);
@@ -586,7 +620,11 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         if (C2P) {
           // The 32 values sit at descending addresses from c_read; read them as 17 aligned 32-bit words and
           // realign odd lanes with a funnel shift (half the shared-memory wavefronts of 16-bit loads).
-          {
+          if (sat) {
+            const float cq = lds_f32(c_row);
+#pragma unroll
+            for (int e = 0; e < KPT; ++e) s[e] += cq;
+          } else {
             const uint32_t lo_addr = (c_read - 2u * (KPT - 1)) & ~3u;
             const uint32_t sh = (uint32_t)(lane & 1) * 16u;
             uint32_t wv[KPT / 2 + 1];
@@ -601,7 +639,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           }
           TL0(11500 + g);
           bar_quadrant(qd);
-          if (has_next) drain_c();
+          if (has_next) drain_c(sat_n);
           TL0(11800 + g);
         }
         // Phase 2.  Scores stay unscaled in s[]; the exponentials are taken at once against the reference exponent
@@ -610,7 +648,30 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const float m_prev = (it > 0) ? m_run : 0.f;
         float mx = -CUDART_INF_F, lsum = 0.f;
         uint32_t pk[KPT / 2];
-        if (nvalid >= KPT) {
+        if (sat) {
+          // Saturated tile: p2c is one value per key (floats at the start of the p2c staging area); masking is
+          // applied unconditionally, this path is not the common one.
+          if (P2C) {
+#pragma unroll
+            for (int v = 0; v < KPT / 4; ++v) {
+              float4 t;
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w)
+                           : "r"(stP + 4u * (uint32_t)(KPT * grp + 4 * v)));
+              s[4 * v] += t.x; s[4 * v + 1] += t.y; s[4 * v + 2] += t.z; s[4 * v + 3] += t.w;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < KPT; e += 2) {
+            const float x0 = (e < nvalid) ? s[e] : -CUDART_INF_F;
+            const float x1 = (e + 1 < nvalid) ? s[e + 1] : -CUDART_INF_F;
+            s[e] = x0; s[e + 1] = x1;
+            mx = fmaxf(mx, fmaxf(x0, x1));
+            const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
+            lsum += a + b;
+            pk[e / 2] = pack_bf16x2(a, b);
+          }
+        } else if (nvalid >= KPT) {
 #pragma unroll
           for (int e = 0; e < KPT; e += 2) {
             float x0 = s[e], x1 = s[e + 1];
@@ -632,7 +693,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
               x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * (e & 31)));
               x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31)));
             }
-            x0 = (e < nvalid) ? x0 : -CUDART_INF_F;
+            x0 = (e < nvalid) ? x0 : -CUDART_INF_F;                      // keys beyond the sequence end
             x1 = (e + 1 < nvalid) ? x1 : -CUDART_INF_F;
             s[e] = x0; s[e + 1] = x1;
             mx = fmaxf(mx, fmaxf(x0, x1));
@@ -648,7 +709,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         sts_f32(x_mine, mx);
         bar_all_cuda_warps();
         TL0(13000 + g);
-        if (has_next) drain_p2();
+        if (has_next) drain_p2(sat_n);
         TL0(13500 + g);
 #pragma unroll
         for (int gg = 0; gg < GROUPS; ++gg) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t)));
@@ -773,16 +834,16 @@ int token_map(CUtensorMap* m, const void* ptr, int64_t tokens, int H, int B, int
   return encode_map(m, ptr, 4, dims, strides, box, what);
 }
 
-int table_map(CUtensorMap* m, const void* ptr, int rows, int H, const char* what) {
+int table_map(CUtensorMap* m, const void* ptr, int rows, int H, int box_rows, const char* what) {
   uint64_t dims[3] = {(uint64_t)HD, (uint64_t)rows, (uint64_t)H};
   uint64_t strides[2] = {(uint64_t)HD * 2, (uint64_t)rows * HD * 2};
-  uint32_t box[3] = {HD, BAND, 1};
+  uint32_t box[3] = {HD, (uint32_t)box_rows, 1};
   return encode_map(m, ptr, 3, dims, strides, box, what);
 }
 
-template <bool C2P, bool P2C>
+template <bool C2P, bool P2C, bool LONG>
 int launch_variant(const AttnParams& p, dim3 grid, const CUtensorMap* maps, cudaStream_t s) {
-  auto kern = attn_umma_kernel<C2P, P2C>;
+  auto kern = attn_umma_kernel<C2P, P2C, LONG>;
   static bool configured = false;           // per instantiation; attribute is per device, set on every device change
   static int configured_dev = -1;
   int dev = 0;
@@ -792,7 +853,7 @@ int launch_variant(const AttnParams& p, dim3 grid, const CUtensorMap* maps, cuda
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
     configured = true; configured_dev = dev;
   }
-  kern<<<grid, NTHREADS, SMEM_BYTES, s>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4]);
+  kern<<<grid, NTHREADS, SMEM_BYTES, s>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6]);
   return cuda_fail(cudaGetLastError(), "attn_umma launch");
 }
 
@@ -838,7 +899,7 @@ size_t umma_workspace_bytes(int n_seqs, int64_t total_tokens) {
 
 int launch_attn_umma(const AttnParams& p, cudaStream_t s) {
   if (p.H > 65535) { set_error("more than 65535 heads"); return TDB_ERR_SHAPE; }
-  CUtensorMap maps[5];
+  CUtensorMap maps[7];
   memset(maps, 0, sizeof(maps));
   const int64_t tokens = p.varlen ? p.total_tokens : p.L;
   const int B = p.varlen ? 1 : p.n_seqs;
@@ -846,10 +907,14 @@ int launch_attn_umma(const AttnParams& p, cudaStream_t s) {
   if ((rc = token_map(&maps[0], p.q, tokens, p.H, B, p.q_sb, p.q_st, p.q_sh, "q"))) return rc;
   if ((rc = token_map(&maps[1], p.k, tokens, p.H, B, p.k_sb, p.k_st, p.k_sh, "k"))) return rc;
   if ((rc = token_map(&maps[2], p.v, tokens, p.H, B, p.v_sb, p.v_st, p.v_sh, "v"))) return rc;
-  if (p.flags & TDB_FLAG_C2P) { if ((rc = table_map(&maps[3], p.kr_exp, p.exp_rows, p.H, "kr_exp"))) return rc; }
-  else maps[3] = maps[0];
-  if (p.flags & TDB_FLAG_P2C) { if ((rc = table_map(&maps[4], p.qr_exp, p.exp_rows, p.H, "qr_exp"))) return rc; }
-  else maps[4] = maps[0];
+  if (p.flags & TDB_FLAG_C2P) {
+    if ((rc = table_map(&maps[3], p.kr_exp, p.exp_rows, p.H, BAND, "kr_exp"))) return rc;
+    if ((rc = table_map(&maps[5], p.kr_exp, p.exp_rows, p.H, SATN, "kr_exp (saturated tiles)"))) return rc;
+  } else { maps[3] = maps[0]; maps[5] = maps[0]; }
+  if (p.flags & TDB_FLAG_P2C) {
+    if ((rc = table_map(&maps[4], p.qr_exp, p.exp_rows, p.H, BAND, "qr_exp"))) return rc;
+    if ((rc = table_map(&maps[6], p.qr_exp, p.exp_rows, p.H, SATN, "qr_exp (saturated tiles)"))) return rc;
+  } else { maps[4] = maps[0]; maps[6] = maps[0]; }
 
   // Persistent CTAs: one per SM (201 KB of shared memory and all 512 tensor-memory columns each), never more
   // than there are work items (query tiles x heads).
@@ -870,10 +935,14 @@ int launch_attn_umma(const AttnParams& p, cudaStream_t s) {
   const int64_t items = tiles * p.H;
   dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
   const bool c2p = p.flags & TDB_FLAG_C2P, p2c = p.flags & TDB_FLAG_P2C;
-  if (c2p && p2c) return launch_variant<true, true>(p, grid, maps, s);
-  if (c2p) return launch_variant<true, false>(p, grid, maps, s);
-  if (p2c) return launch_variant<false, true>(p, grid, maps, s);
-  return launch_variant<false, false>(p, grid, maps, s);
+  // Saturated tiles exist only if a sequence exceeds the saturation distance by a tile; the variant that handles
+  // them specially is a little slower on ordinary tiles, so it is used from twice that length on (p.L is the
+  // padded length or the caller's max_seqlen).
+  const bool lng = (c2p || p2c) && p.L >= 2 * (p.exp_delta_max - TDB_EXPAND_MARGIN) + BK;
+  if (c2p && p2c) return lng ? launch_variant<true, true, true>(p, grid, maps, s) : launch_variant<true, true, false>(p, grid, maps, s);
+  if (c2p) return lng ? launch_variant<true, false, true>(p, grid, maps, s) : launch_variant<true, false, false>(p, grid, maps, s);
+  if (p2c) return lng ? launch_variant<false, true, true>(p, grid, maps, s) : launch_variant<false, true, false>(p, grid, maps, s);
+  return launch_variant<false, false, false>(p, grid, maps, s);
 }
 
 }  // namespace tdb
