@@ -327,27 +327,53 @@ def run_ours(args):
         clocks = sampler.stop(w0, w1)
         clocks["window"] = window
 
-    # ---- end to end through the public op: pinned host buffers in, host buffer out ----
+    # ---- end to end through the reference-facing module call (model.py:34): hidden states in pinned host memory
+    #      -> device -> FlashDisentangledSelfAttention.forward (QKV projections + fused attention) -> host ----
     e2e_ms = None
     h2d = d2h = 0
+    e2e_api = None
     if not args.no_e2e:
-        hq, hk, hv = (t.contiguous().cpu().pin_memory() for t in (q, k, v))
-        hout = torch.empty(q.shape, dtype=dtype).pin_memory()
-        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+        from transformers import DebertaV2Config
+        from turbodeberta_b200.model import FlashDisentangledSelfAttention
+        cfg = DebertaV2Config(hidden_size=w.hidden_size, num_attention_heads=w.num_heads, relative_attention=True,
+                              position_buckets=w.position_buckets, max_relative_positions=w.max_relative_positions,
+                              share_att_key=True, pos_att_type=["c2p", "p2c"], hidden_dropout_prob=0.0,
+                              attention_probs_dropout_prob=0.0, max_position_embeddings=512)
+        mod = FlashDisentangledSelfAttention(cfg).eval()
+        mod.load_state_dict({n: t for n, t in w.params.items() if n in mod.state_dict()})
+        mod = mod.to(dev, dtype)
+        rel_dev = w.rel_embeddings.to(dev, dtype)
+        rel_dev._tdb_stamp = ("bench", 1)           # what the patched encoder does: tables are built once per weights
+        if fixed:
+            hidden_host = w.hidden.to(dtype).pin_memory()                              # [B, L, hidden]
+            mask_dev = (torch.arange(w.padded_len, device=dev)[None, :] < lens[:, None]).to(torch.int32)
+        else:                                                                            # one packed row [1, T, hidden]
+            hidden_host = w.hidden.to(dtype)[None].pin_memory()
+            mask_dev = None
+        hout = torch.empty(hidden_host.shape, dtype=dtype).pin_memory()
+        h2d = hidden_host.numel() * hidden_host.element_size()
         d2h = hout.numel() * hout.element_size()
+        e2e_api = "FlashDisentangledSelfAttention.forward(hidden_states, attention_mask, rel_embeddings=...)"
 
+        @torch.no_grad()
         def e2e_step():
-            dq, dk, dv = (t.to(dev, non_blocking=True) for t in (hq, hk, hv))
+            x = hidden_host.to(dev, non_blocking=True)
             if fixed:
-                oo = step(dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)).permute(0, 2, 1, 3)
-            else:
-                oo = step(dq, dk, dv)
-            hout.copy_(oo, non_blocking=True)
+                y, _ = mod(x, mask_dev, rel_embeddings=rel_dev)
+            else:                                   # packed stream: the op-level call (the module takes padded batches)
+                h = x[0]
+                qq = mod.query_proj(h).view(-1, w.num_heads, w.head_dim)
+                kk = mod.key_proj(h).view(-1, w.num_heads, w.head_dim)
+                vv = mod.value_proj(h).view(-1, w.num_heads, w.head_dim)
+                y = step(qq, kk, vv).reshape(1, -1, w.hidden_size)
+            hout.copy_(y, non_blocking=True)
 
+        if not fixed:
+            e2e_api = "query/key/value_proj + flash_attention_with_disentangled_varlen on the packed stream"
         for _ in range(3):
             e2e_step()
         barrier()
-        n_e2e = max(3, min(args.steps, 10))
+        n_e2e = max(3, min(args.steps, 20))
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(n_e2e):
@@ -390,7 +416,7 @@ def run_ours(args):
         }
         if e2e_ms is not None:
             line["e2e"] = {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_max,
-                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "call": e2e_api}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line), flush=True)
