@@ -79,8 +79,11 @@ TDB_API int tdb_relpos_project(const void* rel, const void* W, const void* bias,
  *   out[h, x, :] = table[h, idx[clamp(x - exp_delta_max, -idx_delta_max, idx_delta_max) + idx_delta_max], :]
  * for x in [0, exp_rows), exp_rows >= 2*exp_delta_max+1.  table [H, two_span, D] of `dtype`.  With it the
  * rows a 128x128 score tile needs are one contiguous window, which the tensor-core kernel loads with a
- * single bulk copy.  No counterpart in the reference, which instead materialises Q.Kr^T and K.Qr^T
- * for every token (model.py:122-125, 143-148). */
+ * single bulk copy.  exp_delta_max must be (saturation distance + TDB_EXPAND_MARGIN), where the saturation distance
+ * is the smallest |delta| from which idx[] no longer changes on either side (max_relative_positions for an even
+ * position_buckets, the span without buckets): the attention kernel derives the saturation distance from
+ * exp_delta_max to recognise tiles whose scores all use one table row.  No counterpart in the reference, which
+ * instead materialises Q.Kr^T and K.Qr^T for every token (model.py:122-125, 143-148). */
 TDB_API int tdb_relpos_expand(const void* table, const int16_t* idx, int idx_delta_max, int H, int two_span,
                       int D, int dtype, int exp_delta_max, int exp_rows, void* out, void* stream);
 
@@ -95,7 +98,9 @@ TDB_API size_t tdb_attn_workspace_bytes(int n_seqs, int64_t total_tokens);
  * seqlens: int32 [B] valid lengths or NULL (all L).  Query rows at or beyond the length are written as zeros.
  * idx: table from tdb_bucket_table; kr_exp/qr_exp: tables from tdb_relpos_expand (needed by the
  * tensor-core kernel; may be NULL for the CUDA-core kernel).  lse: float [B, H, L] or NULL.
- * status: int32[4] device words, zero on entry; word 0 becomes non-zero if a bounded wait gave up. */
+ * status: int32[4] device words, zero on entry; word 0 becomes non-zero if a bounded wait gave up, word 1 if
+ * cu_seqlens was malformed (packed form); word 2 is used by the tensor-core kernel as its work counter (the launch
+ * resets it), word 3 is reserved.  Do not share one status block between launches that can overlap. */
 TDB_API int tdb_attn_fwd_fixed(const void* q, const void* k, const void* v, void* o,
                        int64_t q_sb, int64_t q_st, int64_t q_sh,
                        int64_t k_sb, int64_t k_st, int64_t k_sh,

@@ -12,7 +12,7 @@ LIB = os.path.join(HERE, "libtdb_b200.so")
 SOURCES = ["tdb_api.cu", "tables.cu", "attn_simt.cu", "attn_umma.cu", "relpos_umma.cu"]
 HEADERS = ["tdb_internal.h", "ptx_sm100.cuh", os.path.join("..", "..", "include", "tdb_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 
 def _nvcc() -> str:
@@ -36,7 +36,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB
     nvcc = _nvcc()
     objs = []
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    flags = list(NVCC_FLAGS)
     if verbose:
         flags = flags + ["-Xptxas", "-v"]
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)

@@ -598,6 +598,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         bar_all_cuda_warps();
       }
       float m_run = 0.f, l_part = 0.f;
+      // this thread's slice of the item's output rows (computed here, where its latency hides behind the first tile)
+      __nv_bfloat16* const orow_item = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)cur.bcoord * p.o_sb +
+                                       (cur.tok0 + cur.q0 + row_t) * p.o_st + (int64_t)cur.h * p.o_sh + OPT * grp;
       for (int it = 0; it < cur.n_kv; ++it, ++g) {
         const bool has_next = (it + 1 < cur.n_kv) || item_follows;
         const int nvalid = cur.len - it * BK - KPT * grp;            // keys e >= nvalid of this thread are masked
@@ -765,17 +768,18 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(O_TAKEN));                        // the next item's first P.V may overwrite O
+      TL0(20500 + n_item);
       const int row = cur.q0 + row_t;
-      const float inv = 1.f / l_tot;
+      float inv;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(l_tot));
       if (row < cur.rows) {
         const bool valid = row < cur.len;
         uint32_t outw[OPT / 2];
 #pragma unroll
         for (int e = 0; e < OPT; e += 2)
           outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
-        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)cur.bcoord * p.o_sb +
-                              (cur.tok0 + row) * p.o_st + (int64_t)cur.h * p.o_sh + OPT * grp;
-        uint4* dst = reinterpret_cast<uint4*>(orow);
+        uint4* dst = reinterpret_cast<uint4*>(orow_item);
+        TL0(20700 + n_item);
 #pragma unroll
         for (int i = 0; i < OPT / 8; ++i)
           dst[i] = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
@@ -934,6 +938,8 @@ int launch_attn_umma(const AttnParams& p, cudaStream_t s) {
   }
   const int64_t items = tiles * p.H;
   dim3 grid((unsigned)(items < sms ? items : sms), 1, 1);
+  // status word 2 is the device-wide work counter of this launch; start it at zero even if the caller reuses the words
+  if ((rc = cuda_fail(cudaMemsetAsync(p.status + 2, 0, sizeof(int32_t), s), "cudaMemsetAsync(work counter)"))) return rc;
   const bool c2p = p.flags & TDB_FLAG_C2P, p2c = p.flags & TDB_FLAG_P2C;
   // Saturated tiles exist only if a sequence exceeds the saturation distance by a tile; the variant that handles
   // them specially is a little slower on ordinary tiles, so it is used from twice that length on (p.L is the
