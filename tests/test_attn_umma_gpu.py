@@ -105,3 +105,57 @@ def test_umma_bad_cu_seqlens_reported():
     with pytest.raises(ValueError):
         flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, 64, 64, False, 0.07, 256, 512,
                                                  tables=tables, kernel=UMMA)
+
+
+def test_empty_and_degenerate_inputs():
+    """Empty batches, zero-length sequences inside a packed stream and a fully padded row."""
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+    w = _wl([130, 5], None)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    scale = 1.0 / (3 * 64) ** 0.5
+    # packed stream with empty sequences in front, in the middle and at the end
+    cu = torch.tensor([0, 0, 130, 130, 135, 135], dtype=torch.int32, device="cuda")
+    o = flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, 130, 130, False, scale, 256, 512,
+                                                 tables=tables, kernel=UMMA)
+    ref = util.oracle_varlen(q, k, v, tables, np.array([0, 130, 135]), w, sm_scale=scale)
+    util.assert_close(o, ref, DT, "packed stream with empty sequences")
+    # no tokens at all
+    e = torch.empty(0, 2, 64, dtype=DT, device="cuda")
+    cu0 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert flash_attention_with_disentangled_varlen(e, e, e, None, None, cu0, cu0, 0, 0, False, scale, 256, 512,
+                                                    tables=tables, kernel=UMMA).shape == (0, 2, 64)
+    # empty batch and a batch whose second row is entirely padding
+    eb = torch.empty(0, 2, 16, 64, dtype=DT, device="cuda")
+    assert flash_attention_with_disentangled(eb, eb, eb, None, None, False, scale, 256, 512, tables=tables,
+                                             kernel=UMMA).shape == (0, 2, 16, 64)
+    w2 = _wl([100, 100], 100)
+    q2, k2, v2, rel2, P2 = util.device_inputs(w2, DT)
+    t2 = util.make_tables(w2, rel2, P2)
+    lens = torch.tensor([100, 0], dtype=torch.int32, device="cuda")
+    o2 = flash_attention_with_disentangled(q2.permute(0, 2, 1, 3), k2.permute(0, 2, 1, 3), v2.permute(0, 2, 1, 3), None,
+                                           None, False, scale, 256, 512, seqlens=lens, tables=t2, kernel=UMMA)
+    ref2 = util.oracle_fixed(q2, k2, v2, t2, [100, 0], w2, sm_scale=scale)
+    util.assert_close(o2.permute(0, 2, 1, 3), ref2, DT, "row of padding only")
+    assert torch.count_nonzero(o2[1]).item() == 0
+
+
+def test_strided_views_and_lse():
+    """q, k, v as slices of one fused [B, L, 3, H, D] buffer (non-trivial strides), and the optional LSE output."""
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    w = _wl([200, 77, 129], 200)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    fused = torch.stack([q, k, v], dim=2).contiguous()                     # [B, L, 3, H, D]
+    qs, ks, vs = (fused[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    scale = 1.0 / (3 * 64) ** 0.5
+    lens = torch.as_tensor(np.asarray(w.lengths), dtype=torch.int32, device="cuda")
+    o, lse = flash_attention_with_disentangled(qs, ks, vs, None, None, False, scale, 256, 512, seqlens=lens,
+                                               tables=tables, kernel=UMMA, return_lse=True)
+    ref = util.oracle_fixed(q, k, v, tables, w.lengths, w, sm_scale=scale)
+    util.assert_close(o.permute(0, 2, 1, 3), ref, DT, "strided q/k/v")
+    o2, lse2 = flash_attention_with_disentangled(qs, ks, vs, None, None, False, scale, 256, 512, seqlens=lens,
+                                                 tables=tables, kernel=SIMT, return_lse=True)
+    for b, n in enumerate(w.lengths):
+        assert (lse[b, :, :n] - lse2[b, :, :n]).abs().max().item() < 5e-2

@@ -161,10 +161,11 @@ TDB_API int tdb_attn_fwd_fixed(const void* q, const void* k, const void* v, void
   p.seqlens = seqlens; p.cu_seqlens = nullptr; p.varlen = 0; p.n_seqs = B; p.L = L; p.total_tokens = (int64_t)B * L;
   p.H = H; p.D = D; p.sm_scale = sm_scale; p.flags = flags;
   p.lse = lse; p.lse_sb = (int64_t)H * L; p.lse_sh = L; p.status = status;
+  if (B < 0 || L < 0) { set_error("negative size"); return TDB_ERR_ARG; }
+  if (B == 0 || L == 0) return TDB_OK;     // nothing to compute: pointers of empty tensors may be null
   int rc = check_common(p, dtype, kernel);
   if (rc) return rc;
   if (B > 1 && (q_sb <= 0 || k_sb <= 0 || v_sb <= 0 || o_sb <= 0)) { set_error("batch stride must be positive when B > 1"); return TDB_ERR_ARG; }
-  if (B == 0 || L == 0) return TDB_OK;
   int kn = pick_kernel(dtype, kernel);
   if (kn == TDB_KERNEL_SIMT) return launch_attn_simt(p, dtype, (cudaStream_t)stream);
   if ((rc = check_umma(p, dtype))) return rc;

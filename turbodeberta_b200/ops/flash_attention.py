@@ -111,6 +111,8 @@ class _FixedFn(torch.autograd.Function):
         o = torch.empty((B, L, H, D), dtype=q.dtype, device=dev).permute(0, 2, 1, 3)     # (B,H,L,D) view of [B,L,H,D]
         lse = torch.empty((B, H, L), dtype=torch.float32, device=dev) if return_lse else None
         status = torch.zeros(4, dtype=torch.int32, device=dev)
+        if B == 0 or L == 0:                         # nothing to compute
+            return (o, lse, status)
         if seqlens is not None:
             seqlens = seqlens.to(device=dev, dtype=torch.int32).contiguous()
             if seqlens.numel() != B:

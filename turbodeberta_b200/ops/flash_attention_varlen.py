@@ -39,6 +39,9 @@ class _VarlenFn(torch.autograd.Function):
         cu_seqlens = cu_seqlens.contiguous()
         n_seqs = cu_seqlens.numel() - 1
         o = torch.empty((T, H, D), dtype=q.dtype, device=dev)
+        if T == 0 or n_seqs == 0:                    # nothing to compute
+            st = torch.zeros(4, dtype=torch.int32, device=dev)
+            return (o, torch.empty((H, T), dtype=torch.float32, device=dev) if return_lse else None, st)
         lse = torch.empty((H, T), dtype=torch.float32, device=dev) if return_lse else None
         status = torch.zeros(4, dtype=torch.int32, device=dev)
         ws_bytes = int(cabi.lib.tdb_attn_workspace_bytes(n_seqs, T))
