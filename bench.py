@@ -43,6 +43,9 @@ def parse():
     ap.add_argument("--encoder-batch", type=int, default=256, help="global batch of the encoder workload")
     ap.add_argument("--encoder-layers", type=int, default=24)
     ap.add_argument("--with-eager", action="store_true", help="encoder workload: also time the unpatched eager model on the GPU")
+    ap.add_argument("--encoder-ragged", action="store_true",
+                    help="encoder workload: valid lengths uniform in [64, 512] (right padded) instead of an all-ones mask")
+    ap.add_argument("--no-packing", action="store_true", help="encoder workload: keep padded batches padded")
     ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "umma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -457,6 +460,11 @@ def run_encoder(args):
     sl = sharding.shard_batch(B, world, rank)
     ids = ids_all[sl].pin_memory()
     mask = torch.ones(ids.shape, dtype=torch.long, device=dev)
+    if args.encoder_ragged:
+        lens_all = np.random.default_rng(1004).integers(64, L + 1, B)
+        lens = torch.as_tensor(lens_all[sl], device=dev)
+        mask = (torch.arange(L, device=dev)[None, :] < lens[:, None]).long()
+    model.encoder.pack_padded_batches = not args.no_packing
 
     @torch.no_grad()
     def step(model=model):
@@ -514,7 +522,9 @@ def run_encoder(args):
         line = {"metric": "deberta_v3_large_encoder_seq_per_s", "value": B / (ms * 1e-3), "unit": "seq/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"c4_v3large_{args.encoder_layers}layers_b{B}_l512_allones", "global_batch": B,
+                "config": {"workload": f"c4_v3large_{args.encoder_layers}layers_b{B}_l512_" +
+                           ("ragged64to512" + ("_padded" if args.no_packing else "_packed") if args.encoder_ragged else "allones"),
+                           "global_batch": B,
                            "seq_len": L, "parallelism": f"batch shards x{world}, NCCL all-gather of outputs",
                            "l2": "activations of one step (hundreds of MB) exceed L2"},
                 "e2e": {"value": B / (ms * 1e-3), "unit": "seq/s", "h2d_bytes_per_step": int(ids.numel() * 8),

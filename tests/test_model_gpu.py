@@ -104,3 +104,38 @@ def test_tables_follow_weight_updates():
         fl.encoder.layer[0].attention.self.key_proj.weight.mul_(1.5)
         b = fl(input_ids=ids).last_hidden_state
     assert not torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_packed_encoder_route_matches_padded_route(dtype):
+    """Padded batches run on the packed token stream by default; both routes and the eager model must agree on
+    every valid token, for the last layer and for the intermediate hidden states."""
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DebertaV2Model
+    from turbodeberta_b200.model import FlashDebertaV2Model
+    torch.manual_seed(8)
+    cfg = _cfg(num_hidden_layers=3)
+    hf = DebertaV2Model(cfg).eval()
+    fl = FlashDebertaV2Model(cfg).eval()
+    fl.load_state_dict(hf.state_dict())
+    fl = fl.to("cuda", dtype)
+    ids = torch.randint(0, 500, (4, 300))
+    mask = torch.zeros(4, 300, dtype=torch.long)
+    for b, n in enumerate([300, 17, 129, 256]):
+        mask[b, :n] = 1
+    v = mask.bool()
+    with torch.no_grad():
+        want = hf(input_ids=ids, attention_mask=mask, output_hidden_states=True)
+        assert fl.encoder.pack_padded_batches
+        packed = fl(input_ids=ids.cuda(), attention_mask=mask.cuda(), output_hidden_states=True)
+        fl.encoder.pack_padded_batches = False
+        padded = fl(input_ids=ids.cuda(), attention_mask=mask.cuda(), output_hidden_states=True)
+        fl.encoder.pack_padded_batches = True
+    assert len(packed.hidden_states) == len(want.hidden_states) == 4
+    tol = 2e-4 if dtype == torch.float32 else 6e-2
+    for a, b_, c in zip(packed.hidden_states, padded.hidden_states, want.hidden_states):
+        a, b_ = a.float().cpu(), b_.float().cpu()
+        scale = c[v].abs().max().item()
+        assert (a[v] - c[v]).abs().max().item() / scale < tol
+        assert (a[v] - b_[v]).abs().max().item() / scale < tol
+    assert torch.count_nonzero(packed.last_hidden_state.float().cpu()[~v]).item() == 0
+    assert torch.equal(packed.last_hidden_state, packed.hidden_states[-1])

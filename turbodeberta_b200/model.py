@@ -29,7 +29,16 @@ from transformers.models.deberta_v2.modeling_deberta_v2 import (
 from . import relpos as _relpos
 from .ops.flash_attention import check_pending_status, flash_attention_with_disentangled
 from .ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
-from .padding import _upad_input, pad_input
+from .padding import _get_unpad_data, _upad_input, index_first_axis, pad_input
+
+
+class PackedSequences:
+    """Stands in for the attention mask when the encoder runs on the packed token stream: hidden states are
+    ``[1, T, hidden]`` with the sequences back to back, ``cu_seqlens`` (int32 ``[n_seqs + 1]``) marks them."""
+    __slots__ = ("cu_seqlens", "max_seqlen")
+
+    def __init__(self, cu_seqlens: torch.Tensor, max_seqlen: int):
+        self.cu_seqlens, self.max_seqlen = cu_seqlens, int(max_seqlen)
 
 
 class MaskInfo:
@@ -94,6 +103,30 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
         super().__init__(*args, **kwargs)
         self._tables = None
         self._tables_key = None
+        self._qkv = None
+        self._qkv_key = None
+
+    # -- fused Q/K/V projection ------------------------------------------------------------------
+    def _project_qkv(self, hidden_states: torch.Tensor, query_states: torch.Tensor):
+        """Q, K, V as ``[..., H, D]`` views.  For inference self-attention the three Linear layers run as one GEMM
+        over a cached concatenation of their weights (rebuilt when a weight changes); the result is consumed through
+        strided views, so no copy follows.  With gradients enabled, or a separate query input, the layers run as is."""
+        H, D = self.num_attention_heads, self.attention_head_size
+        lead = hidden_states.shape[:-1]
+        if query_states is hidden_states and not torch.is_grad_enabled():
+            params = (self.query_proj.weight, self.query_proj.bias, self.key_proj.weight, self.key_proj.bias,
+                      self.value_proj.weight, self.value_proj.bias)
+            key = tuple((t.data_ptr(), t._version, t.dtype, t.device) for t in params)
+            if self._qkv is None or self._qkv_key != key:
+                w = torch.cat([params[0], params[2], params[4]], 0).detach()
+                b = torch.cat([params[1], params[3], params[5]], 0).detach()
+                self._qkv, self._qkv_key = (w, b), key
+            qkv = torch.nn.functional.linear(hidden_states, *self._qkv).view(*lead, 3, H, D)
+            return qkv.select(-3, 0), qkv.select(-3, 1), qkv.select(-3, 2)
+        q = self.query_proj(query_states).view(*query_states.shape[:-1], H, D)
+        k = self.key_proj(hidden_states).view(*lead, H, D)
+        v = self.value_proj(hidden_states).view(*lead, H, D)
+        return q, k, v
 
     # -- relative tables ---------------------------------------------------------------------------
     def _relative_tables(self, rel_embeddings: torch.Tensor, dtype: torch.dtype):
@@ -133,18 +166,22 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
         if query_states.shape[1] != L:
             raise NotImplementedError("query and key lengths must match (encoder self-attention)")
         H, D = self.num_attention_heads, self.attention_head_size
-        q = self.query_proj(query_states).view(B, L, H, D)
-        k = self.key_proj(hidden_states).view(B, L, H, D)
-        v = self.value_proj(hidden_states).view(B, L, H, D)
+        q, k, v = self._project_qkv(hidden_states, query_states)
         scale_factor = 1 + int("c2p" in self.pos_att_type) + int("p2c" in self.pos_att_type)
         sm_scale = 1.0 / math.sqrt(D * scale_factor)
         tables = None
         if self.relative_attention:
             rel_embeddings = self.pos_dropout(rel_embeddings)
             tables = self._relative_tables(rel_embeddings, q.dtype)
-        info = analyse_mask(attention_mask, B, L)
         buckets = self.position_buckets if self.relative_attention else 0
         max_rel = self.max_relative_positions if self.relative_attention else 0
+        if isinstance(attention_mask, PackedSequences):                  # packed stream from the encoder: [1, T, hidden]
+            cu = attention_mask.cu_seqlens
+            out = flash_attention_with_disentangled_varlen(
+                q[0], k[0], v[0], None, None, cu, cu, attention_mask.max_seqlen, attention_mask.max_seqlen, False,
+                sm_scale, buckets, max_rel, tables=tables, check_status=False)
+            return (out.reshape(1, L, H * D), None)
+        info = analyse_mask(attention_mask, B, L)
         if info.all_ones or info.right_padded:
             out = flash_attention_with_disentangled(
                 q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), None, None, False, sm_scale,
@@ -188,10 +225,50 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
     def get_rel_pos(self, hidden_states, query_states=None, relative_pos=None):
         return relative_pos
 
-    def forward(self, *args, **kwargs):
-        out = super().forward(*args, **kwargs)
+    #: run padded batches on the packed token stream (unpad once after the embeddings, re-pad once at the end)
+    pack_padded_batches = True
+    #: with packing, re-pad only the last layer's output; earlier entries of ``hidden_states`` stay ``[1, T, hidden]``
+    skip_intermediate_padding = False
+
+    def forward(self, hidden_states, attention_mask, output_hidden_states=True, output_attentions=False,
+                query_states=None, relative_pos=None, return_dict=True):
+        if (self.pack_padded_batches and query_states is None and self.conv is None and not output_attentions
+                and hidden_states.is_cuda and hidden_states.dim() == 3):
+            info = analyse_mask(attention_mask, hidden_states.shape[0], hidden_states.shape[1])
+            if not info.all_ones:
+                out = self._forward_packed(hidden_states, info, output_hidden_states, return_dict)
+                check_pending_status()
+                return out
+        out = super().forward(hidden_states, attention_mask, output_hidden_states=output_hidden_states,
+                              output_attentions=output_attentions, query_states=query_states,
+                              relative_pos=relative_pos, return_dict=return_dict)
         check_pending_status()          # one synchronisation per encoder forward instead of one per layer
         return out
+
+    def _forward_packed(self, hidden_states, info: MaskInfo, output_hidden_states: bool, return_dict: bool):
+        """The layer loop of the HF encoder (``modeling_deberta_v2.py:630-682``) on valid tokens only.  The reference
+        packs and re-pads inside every attention call (``model.py:157-183``); here the whole stack (attention, both
+        projections, FFN, LayerNorms) sees ``[1, T, hidden]`` and padding costs nothing.  Padded positions of the
+        returned tensors are zero."""
+        from transformers.modeling_outputs import BaseModelOutput
+        B, L, hid = hidden_states.shape
+        indices, cu_seqlens, max_seqlen = _get_unpad_data(info.key_mask)
+        x = index_first_axis(hidden_states.reshape(B * L, hid), indices)[None]
+        seqs = PackedSequences(cu_seqlens, max_seqlen)
+        rel_embeddings = self.get_rel_embedding()
+        all_hidden = (hidden_states,) if output_hidden_states else None
+        n = len(self.layer)
+        for i, layer in enumerate(self.layer):
+            x, _ = layer(x, seqs, query_states=None, relative_pos=None, rel_embeddings=rel_embeddings,
+                         output_attentions=False)
+            if output_hidden_states:
+                last = i == n - 1
+                all_hidden = all_hidden + ((pad_input(x[0], indices, B, L) if (last or not self.skip_intermediate_padding)
+                                            else x),)
+        output_states = all_hidden[-1] if output_hidden_states else pad_input(x[0], indices, B, L)
+        if not return_dict:
+            return tuple(v for v in [output_states, all_hidden, None] if v is not None)
+        return BaseModelOutput(last_hidden_state=output_states, hidden_states=all_hidden, attentions=None)
 
     def get_rel_embedding(self):
         if not self.relative_attention:
@@ -225,7 +302,7 @@ def patch_model(model: nn.Module) -> nn.Module:
             old = mod.self
             new = FlashDisentangledSelfAttention.__new__(FlashDisentangledSelfAttention)
             new.__dict__.update(old.__dict__)
-            new._tables, new._tables_key = None, None
+            new._tables, new._tables_key, new._qkv, new._qkv_key = None, None, None, None
             mod.self = new
         if type(mod) is DebertaV2Encoder:
             mod.__class__ = FlashDebertaV2Encoder
