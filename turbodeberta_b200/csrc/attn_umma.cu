@@ -1,30 +1,37 @@
 // Fused disentangled attention on the sm_100a tensor cores (tcgen05 UMMA, accumulators in tensor memory).
 //
-// One CTA = one (sequence, head, 128-query tile); it walks the sequence's keys in tiles of 128:
+// Persistent kernel, one CTA per SM.  A work item is one (sequence, head, 128-query tile); the CTA walks the
+// sequence's keys in tiles of 128:
 //
-//   S  = Q . K^T                         128x128      UMMA  (A = Q tile, B = K tile, both K-major in smem)
-//   C  = Q . KrX[win]^T                  2 x 128x128  UMMA  content->position band, as two column halves
-//   P2 = K . QrX[win]^T                  2 x 128x128  UMMA  position->content band (rows = keys), two halves
+//   S  = Q . K^T                         128x128   UMMA  (A = Q tile, B = K tile, both K-major in smem)
+//   C  = Q . KrX[win]^T                  128x256   UMMA  content->position band
+//   P2 = K . QrX[win]^T                  128x256   UMMA  position->content band (rows = keys)
 //   s[i][j] = (S[i][j] + C[i][i-j+127] + P2[j][i-j+127]) * scale ;  mask ;  online softmax
-//   O += P . V                           128x64       UMMA  (A = P as bf16 in tensor memory, B = V tile, MN-major)
+//   O += P . V                           128x64    UMMA  (A = P as bf16 in tensor memory, B = V tile, MN-major)
 //
 // KrX / QrX are the distance-expanded tables (row x <-> distance x - exp_delta_max), so the rows a tile
 // needs are the contiguous window win = [q0 - k0 - 127 + exp_delta_max, +256), one TMA box.  The diagonal
 // read C[i][i-j+127] cannot be done from registers (the column depends on the lane), so both bands are
-// drained from tensor memory to shared memory as bf16 rows and read back skewed.
+// drained from tensor memory to shared memory as bf16 rows and read back skewed.  Tiles whose distances are all
+// saturated need one value per query row / per key instead of a band (long-sequence variant of the kernel).
 //
-// Warp roles (576 threads): warps 0-15 do the CUDA-core work; warp w owns tensor-memory lanes 32*(w%4)..+31
+// Warp roles (608 threads): warps 0-15 do the CUDA-core work; warp w owns tensor-memory lanes 32*(w%4)..+31
 // (query rows, or key rows of P2) and column group w/4, i.e. four threads share a query row and each handles 32
-// of the 128 keys, which puts four warps on every scheduler to hide latency.  Warp 16 = TMA producer (lane 0:
-// tables and K; lane 1: Q and V), warp 17 = tensor-memory allocation + MMA issue (one lane).
+// of the 128 keys, which puts four warps on every scheduler to hide latency.  Warp 16 = TMA producers (lane 0:
+// tables and K, lane 1: V, lane 2: Q), warp 17 = tensor-memory allocation + MMA issue (one lane), warp 18 =
+// scheduler (draws work items from a device-wide counter, publishes them in a shared-memory ring, zeroes tiles
+// that consist of padded rows only).
 //
-// Pipeline: the band halves go through a two-slot ring in tensor memory, so the MMA of one half overlaps the
-// drain of the other, and the bands and S of key tile t+1 are issued while the CUDA warps run the softmax of
-// tile t.  All hand-offs are mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort flag and
-// the status word, after which every role keeps walking its loop without waiting so that the CTA-wide barriers
-// still match, tensor memory is freed, and the host reports TDB_ERR_TIMEOUT.
+// Pipeline: the MMA lane issues C(0) S(0) P2(0) C(1) | S(g+1) P2(g+1) C(g+2) PV(g) | ..., so the bands and scores
+// of the next key tiles are produced while the CUDA warps work on tile g; C and P2 of a tile pass through the one
+// band buffer in tensor memory, each drained to its staging rows before the other is issued.  All hand-offs are
+// mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort flag and the status word, after which
+// every role runs out its loops without waiting (the CUDA warps take their trip counts from one agreed copy of
+// the work item, so their named barriers still match), tensor memory is freed, and the host reports
+// TDB_ERR_TIMEOUT.
 //
-// Tensor-memory columns: [0,128) S, [128,192) O, [192,320) ring slot A, [320,448) ring slot B, [448,512) P (bf16).
+// Tensor-memory columns: [0,128) S, [128,192) O, [192,448) band buffer (two 128-column halves with their own
+// full/free barriers), [448,512) P (bf16).
 #include "tdb_internal.h"
 #include "ptx_sm100.cuh"
 #include <cudaTypedefs.h>
