@@ -43,12 +43,12 @@ using namespace ptx;
 
 namespace {
 
-constexpr int BQ = 128, BK = 128, HD = 64, BAND = 256, HALF = 128;
+constexpr int BQ = 128, BK = 128, HD = 64, BAND = 256;
 #ifndef TDB_GROUPS
 #define TDB_GROUPS 4
 #endif
 constexpr int GROUPS = TDB_GROUPS;              // threads per query row (2 or 4)
-static_assert(GROUPS == 2 || GROUPS == 4, "two or four threads per query row");
+static_assert(GROUPS == 4, "four threads per query row (the drain split and the staging windows assume it)");
 constexpr int KPT = BK / GROUPS;                // keys per thread in the softmax
 constexpr int OPT = HD / GROUPS;                // output columns per thread
 constexpr int NCW = 4 * GROUPS;                 // CUDA-core warps
@@ -69,7 +69,7 @@ constexpr uint32_t TM_S = 0, TM_O = 128, TM_RING = 192, TM_P = 448, TM_COLS = 51
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per wait, then give up
 
 enum Bar { Q_FULL = 0 /* Q_FULL + buffer */, Q_FULL1, Q_EMPTY /* Q_EMPTY + buffer */, Q_EMPTY1, K_FULL, K_EMPTY, V_FULL, V_EMPTY, KR_FULL, KR_EMPTY, QR_FULL, QR_EMPTY,
-           S_FULL, S_TAKEN, RING_FULL_A, RING_FULL_B, RING_FREE_A, RING_FREE_B, P_READY, O_FULL,
+           S_FULL, S_TAKEN, BAND_FULL, BAND_FREE, P_READY, O_FULL,
            O_TAKEN, DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
            WORK_EMPTY0, WORK_EMPTY1, WORK_EMPTY2, WORK_EMPTY3, NBARS };
 constexpr int WORK_RING = 4;
@@ -157,6 +157,19 @@ __device__ __forceinline__ void sts_128(uint32_t addr, uint32_t a, uint32_t b, u
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void bar_all_cuda_warps() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
+// The same barrier with an OR-reduction of one predicate per thread.
+__device__ __forceinline__ bool bar_all_cuda_warps_or(bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "bar.red.or.pred p, 1, %2, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}"
+      : "=r"(r) : "r"((uint32_t)flag), "n"(NCT) : "memory");
+  return r != 0;
+}
 __device__ __forceinline__ void bar_quadrant(int qd) { asm volatile("bar.sync %0, %1;" ::"r"(2 + qd), "n"(GROUPS * 32) : "memory"); }
 
 // N consecutive 32-bit columns of this thread's tensor-memory lane (N = 16, 32 or 64).
@@ -269,7 +282,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < NBARS; ++i) {
-      const bool by_warps = (i == S_TAKEN || i == RING_FREE_A || i == RING_FREE_B || i == P_READY || i == O_TAKEN);
+      const bool by_warps = (i == S_TAKEN || i == BAND_FREE || i == P_READY || i == O_TAKEN);
       const bool by_readers = (i >= WORK_EMPTY0 && i <= WORK_EMPTY3);
       mbar_init(bar(i), by_readers ? (uint32_t)WORK_READERS : (by_warps ? (uint32_t)NCW : 1u));
     }
@@ -411,8 +424,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
       const uint64_t dKr = smem_desc_sw128(sKr), dQr = smem_desc_sw128(sQr);
       const uint32_t tS = tmem + TM_S, tO = tmem + TM_O, tP = tmem + TM_P;
-      const uint32_t tRing[2] = {tmem + TM_RING, tmem + TM_RING + HALF};
-      int fills[2] = {0, 0};               // how often each ring slot has been filled so far
+      const uint32_t tBand = tmem + TM_RING;
+      int fills = 0;                       // how often the band buffer has been filled so far
 
       // A position in this CTA's stream of key tiles: ring index of the work item, key tile inside it.
       struct TileCur { int n, it, n_kv, q0; bool ok; };
@@ -430,13 +443,11 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         if (c.it == 0) wait(Q_FULL + (c.n & 1), (uint32_t)((c.n >> 1) & 1));
       };
       auto wait_ring_free = [&]() {
-        if (fills[0] > 0) wait(RING_FREE_A, (uint32_t)((fills[0] - 1) & 1));
-        if (fills[1] > 0) wait(RING_FREE_B, (uint32_t)((fills[1] - 1) & 1));
+        if (fills > 0) wait(BAND_FREE, (uint32_t)((fills - 1) & 1));
       };
       auto ring_filled = [&]() {
-        tc_commit(bar(RING_FULL_A));
-        tc_commit(bar(RING_FULL_B));
-        ++fills[0]; ++fills[1];
+        tc_commit(bar(BAND_FULL));
+        ++fills;
       };
       // content->position band of key tile g (global count): one 256-column product into the band buffer
       auto issue_c = [&](const TileCur& c, int g) {
@@ -447,7 +458,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
         const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dQc + 2 * k, dKr + 2 * k, idesc, k > 0);
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dQc + 2 * k, dKr + 2 * k, idesc, k > 0);
         ring_filled();
         tc_commit(bar(KR_EMPTY));
         TDB_TL(1, 1000 + g);
@@ -473,7 +484,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           tc_fence_after();
           const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss(tRing[0], dK + 2 * k, dQr + 2 * k, idesc, k > 0);
+          for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dK + 2 * k, dQr + 2 * k, idesc, k > 0);
           ring_filled();
           tc_commit(bar(QR_EMPTY));
         }
@@ -533,7 +544,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     const uint32_t tS = tmem + lane_base + TM_S + KPT * grp;
     const uint32_t tO = tmem + lane_base + TM_O + OPT * grp;
     const uint32_t tP = tmem + lane_base + TM_P + (KPT / 2) * grp;
-    const uint32_t tRingMine = tmem + lane_base + TM_RING + (HALF / GROUPS) * grp;  // + HALF for slot B
     const float sl2 = p.sm_scale * 1.4426950408889634f;
     // staging rows: c2p row i holds band columns [32*qd, +160); p2c row j holds band columns [96 - 32*(j/32), +160)
     const uint32_t c_row = stC + (uint32_t)row_t * STG_STRIDE;
@@ -541,40 +551,47 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     const uint32_t c_read = c_row + 2u * (uint32_t)(lane + (BK - 1) - KPT * grp);          // key e of this thread: c_read - 2e
     const uint32_t p_read = stP + (uint32_t)(KPT * grp) * STG_STRIDE + 2u * (uint32_t)(row_t + 31);  // + e*STRIDE - 2*(e%32)
     const uint32_t x_mine = sX + 4u * (uint32_t)(grp * BQ + row_t);
-    int drains[2] = {0, 0};
+    int drains = 0;
 
-    // Drain one band half from ring slot `half`.  kind 0: c2p (window starts at 32*qd), kind 1: p2c (96 - 32*qd).
-    auto drain_half = [&](int half, int kind, bool sat) {
-      wait(half ? RING_FULL_B : RING_FULL_A, (uint32_t)(drains[half] & 1));
-      ++drains[half];
+    // Drain the band buffer into this warp's share of the staging rows.  kind 0: c2p (window starts at 32*qd),
+    // kind 1: p2c (96 - 32*qd).
+    auto drain_band = [&](int kind, bool sat) {
+      wait(BAND_FULL, (uint32_t)(drains & 1));
+      ++drains;
       tc_fence_after();
       if (sat) {                                                       // one value per row: column 0 of the band
-        if (half == 0 && grp == 0) {
+        if (grp == 0) {
           uint32_t r[16];
           tmem_ld_cols<16>(tmem + lane_base + TM_RING, r);
           sts_f32(kind == 0 ? c_row : stP + 4u * (uint32_t)row_t, __uint_as_float(r[0]));
         }
-      } else
-#pragma unroll
-      for (int c = 0; c < HALF / GROUPS / 32; ++c) {
-        const int col = HALF * half + (HALF / GROUPS) * grp + 32 * c;  // band column of this 32-column chunk
-        const int local = col - (kind == 0 ? 32 * qd : 96 - 32 * qd);  // position inside the staging row
-        if (local >= 0 && local + 32 <= STG_COLS)
-          drain_chunk(tRingMine + (uint32_t)(HALF * half + 32 * c), (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local);
+      } else {
+        // The 160 staged columns of a row are split evenly over the four warps that own the row: 40 columns each.
+        const int local = (STG_COLS / GROUPS) * grp;                   // position inside the staging row
+        const uint32_t src = tmem + lane_base + TM_RING + (uint32_t)((kind == 0 ? 32 * qd : 96 - 32 * qd) + local);
+        const uint32_t dst = (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local;
+        drain_chunk(src, dst);
+        uint32_t r[8];
+        tmem_ld8(src + 32, r);
+        tmem_ld_wait8(r);
+        sts_128(dst + 64, pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+                pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+                pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(half ? RING_FREE_B : RING_FREE_A));
+      if (lane == 0) mbar_arrive(bar(BAND_FREE));
     };
-    auto drain_c = [&](bool sat) { if (C2P) { drain_half(0, 0, sat); drain_half(1, 0, sat); } };
-    auto drain_p2 = [&](bool sat) { if (P2C) { drain_half(0, 1, sat); drain_half(1, 1, sat); } };
+    auto drain_c = [&](bool sat) { if (C2P) drain_band(0, sat); };
+    auto drain_p2 = [&](bool sat) { if (P2C) drain_band(1, sat); };
 
 #define TL0(evt) do { if (tid == 0) TDB_TL(0, evt); } while (0)
     TL0(1);
     struct CurItem { Work k; int next_q0; int has_next; };
     volatile CurItem* cur_shared = reinterpret_cast<volatile CurItem*>(gbase + OFF_CUR);
     Work cur;
-    int g = 0, n_item = 0;
+    int g = 0;
     for (int n = 0;; ++n) {
       // One thread reads the ring (this item, and whether another one follows); everybody else takes its copy
       // after the barrier, so that all 16 warps agree on the trip counts below even after an abort.
@@ -716,32 +733,36 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         // be drained into them right away, which frees tensor memory for the MMA warp early) and publishes the
         // per-thread maxima for the row maximum over the four threads of a row.
         TL0(12000 + g);
+        // Only when some thread of the CTA saw a score far from the reference exponent do the rows exchange their
+        // maxima and move the exponent (the barrier carries the vote); otherwise the exponent simply stays.
+        const float excess_t = fmaf(mx, sl2, -m_prev);
+        const bool vote = (excess_t > 8.f) || (it == 0 && excess_t < -64.f && mx > -CUDART_INF_F);
         sts_f32(x_mine, mx);
-        bar_all_cuda_warps();
+        const bool moved = bar_all_cuda_warps_or(vote);
         TL0(13000 + g);
-        if (has_next) drain_p2(sat_n);
-        TL0(13500 + g);
-#pragma unroll
-        for (int gg = 0; gg < GROUPS; ++gg) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t)));
-        const float row_max = mx * sl2;                                // sl2 > 0
-        const float excess = row_max - m_prev;
-        const bool redo = (excess > 8.f) || (it == 0 && excess < -64.f);
         float m_new = m_prev, alpha = 1.f;
-        if (redo) {
-          m_new = row_max;
-          alpha = ex2(m_prev - m_new);
-          lsum = 0.f;
+        if (moved) {
 #pragma unroll
-          for (int e = 0; e < KPT; e += 2) {
-            const float a = ex2(fmaf(s[e], sl2, -m_new)), b = ex2(fmaf(s[e + 1], sl2, -m_new));
-            lsum += a + b;
-            pk[e / 2] = pack_bf16x2(a, b);
+          for (int gg = 0; gg < GROUPS; ++gg) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t)));
+          const float row_max = mx * sl2;                              // sl2 > 0
+          const float excess = row_max - m_prev;
+          const bool redo = (excess > 8.f) || (it == 0 && excess < -64.f);
+          if (redo) {
+            m_new = row_max;
+            alpha = ex2(m_prev - m_new);
+            lsum = 0.f;
+#pragma unroll
+            for (int e = 0; e < KPT; e += 2) {
+              const float a = ex2(fmaf(s[e], sl2, -m_new)), b = ex2(fmaf(s[e + 1], sl2, -m_new));
+              lsum += a + b;
+              pk[e / 2] = pack_bf16x2(a, b);
+            }
           }
         }
         if (it > 0) {
           wait(O_FULL, (uint32_t)((g - 1) & 1));
           tc_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          if (moved && __any_sync(0xffffffffu, alpha != 1.f)) {
             uint32_t r[OPT];
             tmem_ld_cols<OPT>(tO, r);
 #pragma unroll
@@ -758,6 +779,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_READY));
         TL0(15000 + g);
+        if (has_next) drain_p2(sat_n);                                 // p2c staging rows are free since the barrier above
+        TL0(15500 + g);
         bar_all_cuda_warps();                                          // next tile's staging complete; exchange buffer free
         TL0(18000 + g);
       }
@@ -768,14 +791,14 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
 #pragma unroll
       for (int gg = 0; gg < GROUPS; ++gg) l_tot += lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t));
       wait(O_FULL, (uint32_t)((g - 1) & 1));
-      TL0(20000 + n_item);
+      TL0(20000 + n);
       tc_fence_after();
       uint32_t r[OPT];
       tmem_ld_cols<OPT>(tO, r);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(O_TAKEN));                        // the next item's first P.V may overwrite O
-      TL0(20500 + n_item);
+      TL0(20500 + n);
       const int row = cur.q0 + row_t;
       float inv;
       asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(l_tot));
@@ -786,7 +809,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         for (int e = 0; e < OPT; e += 2)
           outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
         uint4* dst = reinterpret_cast<uint4*>(orow_item);
-        TL0(20700 + n_item);
+        TL0(20700 + n);
 #pragma unroll
         for (int i = 0; i < OPT / 8; ++i)
           dst[i] = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
@@ -794,8 +817,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           p.lse[(int64_t)cur.bcoord * p.lse_sb + (int64_t)cur.h * p.lse_sh + cur.tok0 + row] =
               valid ? (m_run * 0.6931471805599453f + logf(l_tot)) : 0.f;
       }
-      TL0(21000 + n_item);
-      ++n_item;
+      TL0(21000 + n);
       if (lane == 0) release(n);
     }
   }
