@@ -60,9 +60,11 @@ constexpr uint32_t OFF_Q = 0 /* two buffers */, OFF_K = 32768, OFF_V = 49152, OF
 constexpr uint32_t OFF_STC = 131072, OFF_STP = OFF_STC + BQ * STG_STRIDE, OFF_XCH = OFF_STP + BK * STG_STRIDE;
 constexpr uint32_t OFF_BAR = OFF_XCH + GROUPS * BQ * 4;
 constexpr uint32_t OFF_WORK = OFF_BAR + 256;        // ring of work items published by the scheduler lane
-constexpr uint32_t OFF_CUR = OFF_WORK + 256;        // the CUDA-core warps' agreed copy of their current item
-constexpr uint32_t SMEM_BYTES = OFF_CUR + 64 + 1024;   // + slack for the 1024-byte alignment of the base
-static_assert(OFF_STP % 16 == 0 && OFF_XCH % 16 == 0 && OFF_BAR % 16 == 0, "offsets must stay 16-byte aligned");
+constexpr uint32_t OFF_CUR = OFF_WORK + 256;        // abort flag, tensor-memory base, the CUDA-core warps' copies of their items
+constexpr uint32_t OFF_LX = OFF_CUR + 160;          // row-sum partials of a finished item, [item parity][group][row]
+constexpr uint32_t OFF_MX = OFF_LX + 2 * GROUPS * BQ * 4;   // its reference exponents, [item parity][row]
+constexpr uint32_t SMEM_BYTES = OFF_MX + 2 * BQ * 4 + 1024;   // + slack for the 1024-byte alignment of the base
+static_assert(OFF_STP % 16 == 0 && OFF_XCH % 16 == 0 && OFF_BAR % 16 == 0 && OFF_LX % 16 == 0, "offsets must stay 16-byte aligned");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 constexpr uint32_t TM_S = 0, TM_O = 128, TM_RING = 192, TM_P = 448, TM_COLS = 512;
@@ -70,10 +72,10 @@ constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per wai
 
 enum Bar { Q_FULL = 0 /* Q_FULL + buffer */, Q_FULL1, Q_EMPTY /* Q_EMPTY + buffer */, Q_EMPTY1, K_FULL, K_EMPTY, V_FULL, V_EMPTY, KR_FULL, KR_EMPTY, QR_FULL, QR_EMPTY,
            S_FULL, S_TAKEN, BAND_FULL, BAND_FREE, P_READY, O_FULL,
-           O_TAKEN, DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
+           DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
            WORK_EMPTY0, WORK_EMPTY1, WORK_EMPTY2, WORK_EMPTY3, NBARS };
 constexpr int WORK_RING = 4;
-constexpr int WORK_READERS = 3 + 1 + NCW;       // three producer lanes, the MMA lane, one lane per CUDA-core warp
+constexpr int WORK_READERS = 3 + 1 + 1;         // three producer lanes, the MMA lane, the CUDA-core warps' leader
 static_assert(NBARS * 8 <= 256, "barrier block");
 
 struct TileListHeader { int32_t n_tiles; int32_t pad[3]; };
@@ -152,6 +154,11 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
 }
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ uint4 lds_128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ void sts_128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -273,8 +280,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   const uint32_t sQ = sbase + OFF_Q, sK = sbase + OFF_K, sV = sbase + OFF_V, sKr = sbase + OFF_KR, sQr = sbase + OFF_QR;
   const uint32_t stC = sbase + OFF_STC, stP = sbase + OFF_STP, sX = sbase + OFF_XCH;
   const uint32_t bars = sbase + OFF_BAR;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_CUR + 48);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_CUR + 56);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_CUR);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_CUR + 8);
   Work* work_ring = reinterpret_cast<Work*>(gbase + OFF_WORK);
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
   auto wait = [&](int i, uint32_t parity) { return mbar_wait(bar(i), parity, abort_flag, p.status, 1 + i, WAIT_LIMIT_NS); };
@@ -282,7 +289,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < NBARS; ++i) {
-      const bool by_warps = (i == S_TAKEN || i == BAND_FREE || i == P_READY || i == O_TAKEN);
+      const bool by_warps = (i == S_TAKEN || i == BAND_FREE || i == P_READY);
       const bool by_readers = (i >= WORK_EMPTY0 && i <= WORK_EMPTY3);
       mbar_init(bar(i), by_readers ? (uint32_t)WORK_READERS : (by_warps ? (uint32_t)NCW : 1u));
     }
@@ -491,11 +498,11 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_commit(bar(K_EMPTY));
         TDB_TL(1, 3000 + g);
       };
-      // O += P . V of key tile g; the first one of an item overwrites O, so the previous item must have read it
-      auto issue_pv = [&](const TileCur& c, int g, int item_ordinal) {
+      // O += P . V of key tile g.  The first one of an item overwrites O: the CUDA warps read the previous item's O
+      // before they announce the P of this tile, so P_READY covers that as well.
+      auto issue_pv = [&](const TileCur& c, int g) {
         wait(V_FULL, (uint32_t)(g & 1));
         wait(P_READY, (uint32_t)(g & 1));
-        if (c.it == 0 && item_ordinal > 0) wait(O_TAKEN, (uint32_t)((item_ordinal - 1) & 1));
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
@@ -511,7 +518,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       TileCur cc, cs, cv;                  // c2p stream (two tiles ahead), score/p2c stream (one ahead), P.V stream
       cc.n = 0; cc.it = 0; cur_fetch(cc);
       cs = cc; cv = cc;
-      int gc = 0, gs = 0, gv = 0, items_done = 0;
+      int gc = 0, gs = 0, gv = 0;
       if (cv.ok) {
         if (C2P) { issue_c(cc, gc++); cur_next(cc); }
         issue_s(cs, gs); issue_p2(cs, gs); ++gs;
@@ -524,8 +531,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             issue_s(cs, gs); issue_p2(cs, gs); ++gs;
             if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
           }
-          issue_pv(cv, gv++, items_done);
-          if (cv.it + 1 == cv.n_kv) { release(cv.n); ++items_done; }
+          issue_pv(cv, gv++);
+          if (cv.it + 1 == cv.n_kv) release(cv.n);
           cur_next(cv);
           if (!cv.ok) break;
         }
@@ -588,49 +595,111 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
 
 #define TL0(evt) do { if (tid == 0) TDB_TL(0, evt); } while (0)
     TL0(1);
-    struct CurItem { Work k; int next_q0; int has_next; };
-    volatile CurItem* cur_shared = reinterpret_cast<volatile CurItem*>(gbase + OFF_CUR);
-    Work cur;
-    int g = 0;
-    for (int n = 0;; ++n) {
-      // One thread reads the ring (this item, and whether another one follows); everybody else takes its copy
-      // after the barrier, so that all 16 warps agree on the trip counts below even after an abort.
-      if (tid == 0) {
-        Work k, nk;
-        fetch(n, k);
-        const bool more = k.n_kv > 0 && fetch(n + 1, nk);
-        CurItem* c = const_cast<CurItem*>(cur_shared);
-        c->k = k;
-        c->next_q0 = nk.q0;
-        c->has_next = more ? 1 : 0;
+    // The CUDA-core warps walk one flat stream of key tiles.  Thread 0 copies the work items from the scheduler's
+    // ring into four slots, two items ahead of the one being processed, so that every warp takes its trip counts
+    // from the same copy (also after an abort) and an item switch needs no extra barrier: a slot is written at
+    // least one CTA-wide barrier before anybody reads it, and rewritten only after its last reader has passed one.
+    static_assert(sizeof(Work) == 32, "work items are copied as two 16-byte vectors");
+    const uint32_t slots = sbase + OFF_CUR + 16;                       // four items of 32 bytes
+    volatile Work* const item_slots = reinterpret_cast<volatile Work*>(gbase + OFF_CUR + 16);
+    auto load_item = [&](int n, Work& k) {                             // every field (epilogue)
+      const uint4 a = lds_128(slots + 32u * (uint32_t)(n & 3)), b = lds_128(slots + 32u * (uint32_t)(n & 3) + 16u);
+      k.q0 = (int)a.x; k.len = (int)a.y; k.rows = (int)a.z; k.bcoord = (int)a.w; k.h = (int)b.x; k.n_kv = (int)b.y;
+      k.tok0 = (int64_t)(((uint64_t)b.w << 32) | b.z);
+    };
+    auto leader_publish = [&](int n) {                                 // thread 0 only
+      uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0xffffffffu, 0, 0);   // end marker: n_kv = -1
+      if (n == 0 || item_slots[(n - 1) & 3].n_kv > 0) {                // nothing follows the end marker
+        wait(WORK_FULL0 + (n % WORK_RING), (uint32_t)((n / WORK_RING) & 1));
+        const uint32_t src = sbase + OFF_WORK + 32u * (uint32_t)(n % WORK_RING);
+        a = lds_128(src); b = lds_128(src + 16u);
+        if (*abort_flag) b.y = 0xffffffffu;
+        release(n);
       }
-      bar_all_cuda_warps();
+      sts_128(slots + 32u * (uint32_t)(n & 3), a.x, a.y, a.z, a.w);
+      sts_128(slots + 32u * (uint32_t)(n & 3) + 16u, b.x, b.y, b.z, b.w);
+    };
+    const uint32_t lx_mine = sbase + OFF_LX + 4u * (uint32_t)(grp * BQ + row_t);      // + parity * GROUPS * BQ * 4
+    const uint32_t mx_row = sbase + OFF_MX + 4u * (uint32_t)row_t;                     // + parity * BQ * 4
+
+    // Epilogue of item pn, whose last key tile was number gl of the stream: O / l -> global.  Runs during the first
+    // key tile of the item after it (so the wait for its last P.V product is off the critical path), or at the end.
+    auto finish_item = [&](int pn, int gl) {
+      Work w;
+      load_item(pn, w);
+      const uint32_t par = (uint32_t)(pn & 1);
+      float l_tot = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < GROUPS; ++gg)
+        l_tot += lds_f32(sbase + OFF_LX + 4u * (uint32_t)((par * GROUPS + gg) * BQ + row_t));
+      wait(O_FULL, (uint32_t)(gl & 1));
+      TL0(20000 + pn);
+      tc_fence_after();
+      uint32_t r[OPT];
+      tmem_ld_cols<OPT>(tO, r);
+      tc_fence_before();
+      float inv;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(l_tot));
+      // The normalised rows go through shared memory (the quadrant's part of the p2c staging area, which nobody
+      // uses between the barrier that closed this tile's p2c reads and the next drain) so that each store
+      // instruction writes four whole 128-byte rows instead of 32 separate 16-byte pieces.
       {
-        const CurItem* c = const_cast<const CurItem*>(cur_shared);
-        cur = c->k;
+        const bool valid = w.q0 + row_t < w.len;
+        uint32_t outw[OPT / 2];
+#pragma unroll
+        for (int e = 0; e < OPT; e += 2)
+          outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
+        const uint32_t obuf = stP + (uint32_t)(32 * qd) * STG_STRIDE;          // 32 rows, 144-byte pitch
+        const uint32_t mine = obuf + (uint32_t)lane * 144u + (uint32_t)(OPT * 2 * grp);
+#pragma unroll
+        for (int i = 0; i < OPT / 8; ++i)
+          sts_128(mine + 16u * i, outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
+        bar_quadrant(qd);
+        __nv_bfloat16* const obase = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)w.bcoord * p.o_sb +
+                                     (int64_t)w.h * p.o_sh + 8 * (lane & 7);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int rq = 8 * grp + 4 * i + (lane >> 3);                        // row inside the quadrant
+          const int row = w.q0 + 32 * qd + rq;
+          const uint4 v = lds_128(obuf + (uint32_t)rq * 144u + 16u * (uint32_t)(lane & 7));
+          if (row < w.rows) *reinterpret_cast<uint4*>(obase + (w.tok0 + row) * p.o_st) = v;
+        }
+        if (p.lse && grp == 0) {
+          const int row = w.q0 + row_t;
+          if (row < w.rows)
+            p.lse[(int64_t)w.bcoord * p.lse_sb + (int64_t)w.h * p.lse_sh + w.tok0 + row] =
+                valid ? (lds_f32(mx_row + par * (BQ * 4)) * 0.6931471805599453f + logf(l_tot)) : 0.f;
+        }
+        bar_quadrant(qd);                                                      // the staging rows may be drained into again
       }
-      const bool item_follows = cur_shared->has_next != 0;
-      const int next_q0 = cur_shared->next_q0;
-      if (cur.n_kv <= 0) {
-        if (lane == 0) release(n);
-        break;
-      }
-      if (n == 0) {                                                    // bands of the very first key tile
+      TL0(21000 + pn);
+    };
+
+    if (tid == 0) { leader_publish(0); leader_publish(1); }
+    bar_all_cuda_warps();
+    struct { int q0, len, n_kv; } cur;
+    auto switch_item = [&](int n) {
+      volatile Work* w = item_slots + (n & 3);
+      cur.q0 = w->q0; cur.len = w->len; cur.n_kv = w->n_kv;
+    };
+    switch_item(0);
+    if (cur.n_kv > 0) {
+      if (tid == 0) leader_publish(2);
+      {                                                                // bands of the very first key tile
         const bool sat0 = LONG && tile_saturated(p, cur.q0, 0);
         drain_c(sat0);
         drain_p2(sat0);
         bar_all_cuda_warps();
       }
       float m_run = 0.f, l_part = 0.f;
-      // this thread's slice of the item's output rows (computed here, where its latency hides behind the first tile)
-      __nv_bfloat16* const orow_item = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)cur.bcoord * p.o_sb +
-                                       (cur.tok0 + cur.q0 + row_t) * p.o_st + (int64_t)cur.h * p.o_sh + OPT * grp;
-      for (int it = 0; it < cur.n_kv; ++it, ++g) {
-        const bool has_next = (it + 1 < cur.n_kv) || item_follows;
+      int n = 0, it = 0, g = 0;
+      while (true) {
+        const bool last_of_item = (it + 1 == cur.n_kv);
+        const bool has_next = !last_of_item || item_slots[(n + 1) & 3].n_kv > 0;
         const int nvalid = cur.len - it * BK - KPT * grp;            // keys e >= nvalid of this thread are masked
         const bool sat = LONG && tile_saturated(p, cur.q0, it * BK);   // this key tile, and the one after it
-        const bool sat_n = LONG && ((it + 1 < cur.n_kv) ? tile_saturated(p, cur.q0, (it + 1) * BK)
-                                                        : tile_saturated(p, next_q0, 0));
+        const bool sat_n = LONG && (!last_of_item ? tile_saturated(p, cur.q0, (it + 1) * BK)
+                                                  : tile_saturated(p, item_slots[(n + 1) & 3].q0, 0));
         TL0(10000 + g);
         wait(S_FULL, (uint32_t)(g & 1));
         TL0(11000 + g);
@@ -769,6 +838,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             for (int e = 0; e < OPT; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
             tmem_st_cols<OPT>(tO, r);
           }
+        } else if (n > 0) {
+          finish_item(n - 1, g - 1);       // also frees O and P for this tile's P.V (announced by P_READY below)
         }
         TL0(14000 + g);
         l_part = (it > 0 ? l_part * alpha : 0.f) + lsum;
@@ -781,44 +852,21 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         TL0(15000 + g);
         if (has_next) drain_p2(sat_n);                                 // p2c staging rows are free since the barrier above
         TL0(15500 + g);
+        if (last_of_item) {                                            // what the item's epilogue needs from this thread
+          sts_f32(lx_mine + (uint32_t)(n & 1) * (GROUPS * BQ * 4), l_part);
+          if (grp == 0) sts_f32(mx_row + (uint32_t)(n & 1) * (BQ * 4), m_run);
+        }
         bar_all_cuda_warps();                                          // next tile's staging complete; exchange buffer free
         TL0(18000 + g);
+        ++g;
+        if (!last_of_item) { ++it; continue; }
+        ++n;
+        it = 0;
+        switch_item(n);
+        if (cur.n_kv <= 0) break;
+        if (tid == 0) leader_publish(n + 2);
       }
-      // ---- epilogue of the work item: O / l -> global ----
-      sts_f32(x_mine, l_part);
-      bar_quadrant(qd);
-      float l_tot = 0.f;
-#pragma unroll
-      for (int gg = 0; gg < GROUPS; ++gg) l_tot += lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t));
-      wait(O_FULL, (uint32_t)((g - 1) & 1));
-      TL0(20000 + n);
-      tc_fence_after();
-      uint32_t r[OPT];
-      tmem_ld_cols<OPT>(tO, r);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(O_TAKEN));                        // the next item's first P.V may overwrite O
-      TL0(20500 + n);
-      const int row = cur.q0 + row_t;
-      float inv;
-      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(l_tot));
-      if (row < cur.rows) {
-        const bool valid = row < cur.len;
-        uint32_t outw[OPT / 2];
-#pragma unroll
-        for (int e = 0; e < OPT; e += 2)
-          outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
-        uint4* dst = reinterpret_cast<uint4*>(orow_item);
-        TL0(20700 + n);
-#pragma unroll
-        for (int i = 0; i < OPT / 8; ++i)
-          dst[i] = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
-        if (p.lse && grp == 0)
-          p.lse[(int64_t)cur.bcoord * p.lse_sb + (int64_t)cur.h * p.lse_sh + cur.tok0 + row] =
-              valid ? (m_run * 0.6931471805599453f + logf(l_tot)) : 0.f;
-      }
-      TL0(21000 + n);
-      if (lane == 0) release(n);
+      finish_item(n - 1, g - 1);
     }
   }
 
