@@ -264,12 +264,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   // shared-memory ring that every role reads in the same order.
   const int total_tiles = p.varlen ? reinterpret_cast<const int32_t*>(p.workspace)[0]
                                    : p.n_seqs * ((p.L + BQ - 1) / BQ);
-  {                                      // an earlier CTA gave up: do not start (decided once per CTA)
-    __shared__ int s_skip;
-    if (tid == 0) s_skip = (*reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
-    __syncthreads();
-    if (s_skip) return;
-  }
+  // An earlier CTA gave up: the scheduler lane (which reads the word while the CTA sets itself up) hands out no work.
+  int32_t status_at_start = 0;
+  if (warp == NCW + 2 && lane == 0) status_at_start = *reinterpret_cast<volatile int32_t*>(p.status);
 #ifdef TDB_TIMELINE
   int tl_n[3] = {0, 0, 0};
 #endif
@@ -392,10 +389,16 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     // ================================ scheduler ==============================================
     // Draws work items from the device-wide counter and publishes those with tensor work in the ring; tiles made of
     // padded query rows only (padded form) are zeroed here by the whole warp and never reach the other roles.
+    // The first item of a CTA is its own index (no round trip to the counter before the pipeline can start); the
+    // counter hands out the items after those.
     int n = 0;
+    bool first = true;
     while (true) {
       int w = 0;
-      if (lane == 0) w = *abort_flag ? 0x7fffffff : atomicAdd(p.status + 2, 1);
+      if (lane == 0)
+        w = (*abort_flag || status_at_start != 0) ? 0x7fffffff
+                                                  : (first ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.status + 2, 1));
+      first = false;
       w = __shfl_sync(0xffffffffu, w, 0);
       Work k;
       if (!get_work(p, total_tiles, w, k)) k.n_kv = -1;
