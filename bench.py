@@ -30,7 +30,7 @@ METRIC = "disentangled_attn_algorithmic_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on the default workload,
 # from the ncu capture summarised in profiles/attn_umma_config2.md.
-NCU_TRAFFIC_BYTES = 61.16e6     # profiles/attn_umma_config2.md: 56.34 MB read + 6.25 MB written
+NCU_TRAFFIC_BYTES = 61.16e6     # profiles/attn_umma_config2.md: 56.32 MB read + 4.6..5.1 MB written per launch
 
 
 def parse():
