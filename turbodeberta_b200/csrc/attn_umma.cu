@@ -556,7 +556,10 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     const uint32_t tP = tmem + lane_base + TM_P + (KPT / 2) * grp;
     const float sl2 = p.sm_scale * 1.4426950408889634f;
     // staging rows: c2p row i holds band columns [32*qd, +160); p2c row j holds band columns [96 - 32*(j/32), +160)
-    const uint32_t c_row = stC + (uint32_t)row_t * STG_STRIDE;
+    // c2p rows are laid out in pairs (656 bytes per pair, the odd row 320 bytes in): 16-byte row stores of a warp
+    // hit eight different 16-byte slots, and the skewed 32-bit reads (one row per lane, two bytes further per
+    // lane) hit 32 different banks.
+    const uint32_t c_row = stC + (uint32_t)(row_t >> 1) * 656u + (uint32_t)(row_t & 1) * 320u;
     const uint32_t p_row = stP + (uint32_t)row_t * STG_STRIDE;
     const uint32_t c_read = c_row + 2u * (uint32_t)(lane + (BK - 1) - KPT * grp);          // key e of this thread: c_read - 2e
     const uint32_t p_read = stP + (uint32_t)(KPT * grp) * STG_STRIDE + 2u * (uint32_t)(row_t + 31);  // + e*STRIDE - 2*(e%32)
