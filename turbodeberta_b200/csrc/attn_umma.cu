@@ -24,14 +24,18 @@
 //
 // Pipeline: the MMA lane issues C(0) S(0) P2(0) C(1) | S(g+1) P2(g+1) C(g+2) PV(g) | ..., so the bands and scores
 // of the next key tiles are produced while the CUDA warps work on tile g; C and P2 of a tile pass through the one
-// band buffer in tensor memory, each drained to its staging rows before the other is issued.  All hand-offs are
-// mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort flag and the status word, after which
-// every role runs out its loops without waiting (the CUDA warps take their trip counts from one agreed copy of
-// the work item, so their named barriers still match), tensor memory is freed, and the host reports
-// TDB_ERR_TIMEOUT.
+// band buffer in tensor memory (one full/free barrier pair), each drained to its staging rows - 40 columns per
+// warp - before the other is issued.  The CUDA warps walk one flat stream of key tiles across work items: per
+// tile they add the c2p term, drain C of the next tile, add the p2c term and take the exponentials against the
+// reference exponent of the tiles before (a voting barrier tells whether any row has to move it), store P and
+// drain P2 of the next tile.  The epilogue of an item (O / l, staged in shared memory so that whole 128-byte rows
+// are stored) runs inside the first tile of the next item, where the wait for its last P.V product costs nothing.
+// All hand-offs are mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort flag and the status
+// word, after which every role runs out its loops without waiting (the CUDA warps take their trip counts from
+// one copy of the work items kept by thread 0, so their named barriers still match), tensor memory is freed, and
+// the host reports TDB_ERR_TIMEOUT.
 //
-// Tensor-memory columns: [0,128) S, [128,192) O, [192,448) band buffer (two 128-column halves with their own
-// full/free barriers), [448,512) P (bf16).
+// Tensor-memory columns: [0,128) S, [128,192) O, [192,448) band buffer, [448,512) P (bf16).
 #include "tdb_internal.h"
 #include "ptx_sm100.cuh"
 #include <cudaTypedefs.h>
