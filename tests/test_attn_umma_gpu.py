@@ -159,3 +159,33 @@ def test_strided_views_and_lse():
                                                  tables=tables, kernel=SIMT, return_lse=True)
     for b, n in enumerate(w.lengths):
         assert (lse[b, :, :n] - lse2[b, :, :n]).abs().max().item() < 5e-2
+
+
+@pytest.mark.parametrize("mode", ["large", "negative", "rising"])
+def test_umma_reference_exponent_moves(mode):
+    """Scores far from zero: the rows have to move their reference exponent (first tile far below zero, later tiles
+    far above the earlier ones), which rescales the running output; the small-score cases above never get there."""
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    w = _wl([512, 300], 512, hidden=128, heads=2, seed=77)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    if mode == "large":                       # log2-scaled scores with a spread of tens
+        q = (q.float() * 6.0).to(DT)
+    elif mode == "negative":                  # every score of a row far below zero
+        q = (torch.ones_like(q).float() + 0.05 * q.float()).to(DT)
+        k = (-10.0 * torch.ones_like(k).float() + k.float()).to(DT)
+    else:                                     # scores grow with the key position: every key tile raises the maximum
+        ramp = torch.linspace(0.0, 4.0, k.shape[1], device=k.device)[None, :, None, None]
+        q = (torch.ones_like(q).float() + 0.05 * q.float()).to(DT)
+        k = (ramp * torch.ones_like(k).float() + 0.1 * k.float()).to(DT)
+    scale = 1.0 / (3 * 64) ** 0.5
+    lens = torch.as_tensor(np.asarray(w.lengths), dtype=torch.int32, device="cuda")
+    o, lse = flash_attention_with_disentangled(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                               None, None, False, scale, 256, 512, seqlens=lens, tables=tables,
+                                               kernel=UMMA, return_lse=True)
+    ref = util.oracle_fixed(q, k, v, tables, w.lengths, w, sm_scale=scale)
+    util.assert_close(o.permute(0, 2, 1, 3), ref, DT, f"exponent moves ({mode})")
+    o2 = flash_attention_with_disentangled(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                           None, None, False, scale, 256, 512, seqlens=lens, tables=tables, kernel=SIMT)
+    assert (o.float() - o2.float()).abs().max().item() < 2e-2
+    assert torch.isfinite(lse).all()
