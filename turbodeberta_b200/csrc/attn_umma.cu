@@ -752,7 +752,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         // of the previous tiles (0 on the first tile) so that the MUFU work overlaps the shared-memory reads, and
         // are redone only for rows whose new maximum is more than 2^8 above (or, on the first tile, 2^64 below) it.
         const float m_prev = (it > 0) ? m_run : 0.f;
-        float mx = -CUDART_INF_F, lsum = 0.f;
+        float lsum = 0.f;
         uint32_t pk[KPT / 2];
         if (sat) {
           // Saturated tile: p2c is one value per key (floats at the start of the p2c staging area); masking is
@@ -772,7 +772,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             const float x0 = (e < nvalid) ? s[e] : -CUDART_INF_F;
             const float x1 = (e + 1 < nvalid) ? s[e + 1] : -CUDART_INF_F;
             s[e] = x0; s[e + 1] = x1;
-            mx = fmaxf(mx, fmaxf(x0, x1));
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
@@ -786,7 +785,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
               x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31)));
             }
             s[e] = x0; s[e + 1] = x1;
-            mx = fmaxf(mx, fmaxf(x0, x1));
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
@@ -802,25 +800,27 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             x0 = (e < nvalid) ? x0 : -CUDART_INF_F;                      // keys beyond the sequence end
             x1 = (e + 1 < nvalid) ? x1 : -CUDART_INF_F;
             s[e] = x0; s[e + 1] = x1;
-            mx = fmaxf(mx, fmaxf(x0, x1));
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
           }
         }
         // The barrier below closes the reads of the p2c staging rows of this key tile (so the next tile's band can
-        // be drained into them right away, which frees tensor memory for the MMA warp early) and publishes the
-        // per-thread maxima for the row maximum over the four threads of a row.
+        // be drained into them) and carries a vote: only when some thread of the CTA saw a score far from the
+        // reference exponent do the rows exchange their maxima and move the exponent; otherwise it simply stays.
         TL0(12000 + g);
-        // Only when some thread of the CTA saw a score far from the reference exponent do the rows exchange their
-        // maxima and move the exponent (the barrier carries the vote); otherwise the exponent simply stays.
-        const float excess_t = fmaf(mx, sl2, -m_prev);
-        const bool vote = (excess_t > 8.f) || (it == 0 && excess_t < -64.f && mx > -CUDART_INF_F);
-        sts_f32(x_mine, mx);
+        // The vote reads the row sums: an exponential above 2^8 (or an overflow) shows as a large sum, a first tile
+        // far below the exponent as a vanishing one.  The maxima themselves are only formed when the vote passes.
+        const bool vote = (lsum > 256.f) || (it == 0 && nvalid > 0 && lsum < 1.7e-18f);
         const bool moved = bar_all_cuda_warps_or(vote);
         TL0(13000 + g);
         float m_new = m_prev, alpha = 1.f;
         if (moved) {
+          float mx = -CUDART_INF_F;
+#pragma unroll
+          for (int e = 0; e < KPT; ++e) mx = fmaxf(mx, s[e]);
+          sts_f32(x_mine, mx);
+          bar_all_cuda_warps();
 #pragma unroll
           for (int gg = 0; gg < GROUPS; ++gg) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t)));
           const float row_max = mx * sl2;                              // sl2 > 0
