@@ -43,7 +43,7 @@ enum {
 enum { TDB_DTYPE_F32 = 0, TDB_DTYPE_BF16 = 1 };
 
 /* which position terms are added to the content score (pos_att_type, model.py:84-90) */
-enum { TDB_FLAG_C2P = 1, TDB_FLAG_P2C = 2 };
+enum { TDB_FLAG_C2P = 1, TDB_FLAG_P2C = 2, TDB_FLAG_P2C_MIRRORED = 4 /* only with materialised scores */ };
 
 /* kernel selection: AUTO = tensor-core (tcgen05) kernel for bf16, CUDA-core kernel for f32. */
 enum { TDB_KERNEL_AUTO = 0, TDB_KERNEL_SIMT = 1, TDB_KERNEL_UMMA = 2 };
@@ -154,6 +154,32 @@ TDB_API int tdb_attn_fwd_varlen_static(const void* q, const void* k, const void*
                         const void* kr_exp, const void* qr_exp, int exp_delta_max, int exp_rows,
                         const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, int max_seqlen,
                         int H, int D, float sm_scale, int flags, int dtype, int kernel,
+                        float* lse, int32_t* status, void* stream);
+
+/* Legacy operator form (reference ops/flash_attention.py:345-369 and ops/flash_attention_varlen.py:348-374 called with
+ * the MATERIALISED position scores of model.py:122-125 / 143-148): c2p_scores[b, h, t, r] = Q[t].Kr[r] and
+ * p2c_scores[b, h, t, r] = K[t].Qr[r] (rows of two_span contiguous elements of the I/O dtype; either may be null with
+ * its flag clear).  The kernel only gathers them: score[q,k] = (Q[q].K[k] + c2p_scores[q, idx(q-k)] + p2c_scores[k,
+ * idx(q-k)]) * sm_scale, the eager module's convention (HF modeling_deberta_v2.py:315-343); with
+ * TDB_FLAG_P2C_MIRRORED the p2c term is read at idx(k-q) instead, which is what the reference's own kernel does
+ * (ops/flash_attention.py:126-132).  CUDA-core kernel, f32 or bf16; a compatibility path, not a throughput path --
+ * the fused entry points above exist to avoid these tensors.  Strides in elements; other arguments as above. */
+TDB_API int tdb_attn_fwd_fixed_scores(const void* q, const void* k, const void* v, void* o,
+                        int64_t q_sb, int64_t q_st, int64_t q_sh, int64_t k_sb, int64_t k_st, int64_t k_sh,
+                        int64_t v_sb, int64_t v_st, int64_t v_sh, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                        const void* c2p_scores, int64_t c2p_sb, int64_t c2p_st, int64_t c2p_sh,
+                        const void* p2c_scores, int64_t p2c_sb, int64_t p2c_st, int64_t p2c_sh,
+                        int two_span, const int16_t* idx, int idx_delta_max,
+                        const int32_t* seqlens, int B, int L, int H, int D, float sm_scale, int flags, int dtype,
+                        float* lse, int32_t* status, void* stream);
+TDB_API int tdb_attn_fwd_varlen_scores(const void* q, const void* k, const void* v, void* o,
+                        int64_t q_st, int64_t q_sh, int64_t k_st, int64_t k_sh, int64_t v_st, int64_t v_sh,
+                        int64_t o_st, int64_t o_sh,
+                        const void* c2p_scores, int64_t c2p_st, int64_t c2p_sh,
+                        const void* p2c_scores, int64_t p2c_st, int64_t p2c_sh,
+                        int two_span, const int16_t* idx, int idx_delta_max,
+                        const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, int max_seqlen,
+                        int H, int D, float sm_scale, int flags, int dtype,
                         float* lse, int32_t* status, void* stream);
 
 #ifdef __cplusplus

@@ -159,6 +159,40 @@ def attention_single(q, k, v, kr, qr, *, position_buckets, max_relative_position
     return out
 
 
+def attention_single_scores(q, k, v, c2p_scores, p2c_scores, *, position_buckets, max_relative_positions,
+                            sm_scale=None, p2c_mirrored=False, dtype=np.float64):
+    """ONE sequence, legacy operator form: the position products arrive materialised, ``c2p_scores[t, h, r] =
+    Q[t].Kr[r]`` and ``p2c_scores[t, h, r] = K[t].Qr[r]`` (``model.py:122-125``), and are only gathered.
+
+    score[q,k] = (Q[q].K[k] + c2p_scores[q, idx(q-k)] + p2c_scores[k, idx(q-k)]) * sm_scale   (HF:315-343)
+    With ``p2c_mirrored`` the last term is read at ``idx(k-q)``, the index the reference kernel forms
+    (``ops/flash_attention.py:126-132``: ``-bucket(q-k) + span``; the bucket function is odd).
+    q, k, v ``[L, H, d]``; scores ``[L, H, 2*span]`` or None.  Returns ``[L, H, d]``."""
+    q = np.asarray(q, dtype); k = np.asarray(k, dtype); v = np.asarray(v, dtype)
+    L, H, d = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d * (1 + int(c2p_scores is not None) + int(p2c_scores is not None)))
+    out = np.empty((L, H, d), dtype)
+    if L == 0:
+        return out
+    pos = np.arange(L, dtype=np.int64)
+    idx = gather_index(pos[:, None] - pos[None, :], position_buckets, max_relative_positions)  # [a, b] -> idx(a-b)
+    for h in range(H):
+        s = q[:, h, :] @ k[:, h, :].T
+        if c2p_scores is not None:
+            s = s + np.take_along_axis(np.asarray(c2p_scores, dtype)[:, h, :], idx, axis=1)
+        if p2c_scores is not None:
+            full = np.asarray(p2c_scores, dtype)[:, h, :]                      # [Lk, 2span], row = key
+            by_key = idx if p2c_mirrored else idx.T                            # [k, q] -> idx(k-q) or idx(q-k)
+            s = s + np.take_along_axis(full, by_key, axis=1).T
+        s = s * dtype(sm_scale)
+        s = s - s.max(axis=1, keepdims=True)
+        p = np.exp(s)
+        p = p / p.sum(axis=1, keepdims=True)
+        out[:, h, :] = p @ v[:, h, :]
+    return out
+
+
 def attention_varlen(q, k, v, kr, qr, cu_seqlens, **kw):
     """Packed form: q, k, v ``[T, H, d]``; ``cu_seqlens`` int ``[B+1]``.  Relative positions restart
     at every sequence (``ops/flash_attention_varlen.py:70,118``).  Returns ``[T, H, d]``."""

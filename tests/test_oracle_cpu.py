@@ -107,3 +107,28 @@ def test_flop_accounting():
     w = workloads.config2()
     assert w.flops() == orc.algorithmic_flops(w.lengths, 12, 64, 512)
     assert w.bytes(2) == orc.algorithmic_bytes(int(w.lengths.sum()), 12, 64, 512, 2, 32)
+
+
+def test_materialised_scores_form_equals_table_form():
+    """Gathering from materialised Q.Kr^T / K.Qr^T (the reference's operator interface, model.py:122-125) is the
+    same arithmetic as the table form; the mirrored index differs from it exactly where idx(q-k) != idx(k-q)."""
+    rng = np.random.default_rng(5)
+    L, H, d, span = 70, 2, 64, 16
+    q, k, v = (rng.standard_normal((L, H, d)) for _ in range(3))
+    kr, qr = (0.3 * rng.standard_normal((H, 2 * span, d)) for _ in range(2))
+    c2p = np.einsum("lhd,hrd->lhr", q, kr)
+    p2c = np.einsum("lhd,hrd->lhr", k, qr)
+    kw = dict(position_buckets=span, max_relative_positions=64)
+    ref = orc.attention_single(q, k, v, kr, qr, **kw)
+    got = orc.attention_single_scores(q, k, v, c2p, p2c, **kw)
+    np.testing.assert_allclose(got, ref, rtol=0, atol=1e-12)
+    only_c2p = orc.attention_single_scores(q, k, v, c2p, None, sm_scale=0.1, **kw)
+    np.testing.assert_allclose(only_c2p, orc.attention_single(q, k, v, kr, None, p2c=False, sm_scale=0.1, **kw), atol=1e-12)
+    mirrored = orc.attention_single_scores(q, k, v, c2p, p2c, p2c_mirrored=True, **kw)
+    assert np.abs(mirrored - ref).max() > 1e-3
+    # mirrored p2c of (q, k) equals the plain p2c with the roles of the distance swapped: check one element by hand
+    idx = orc.gather_index(np.arange(L)[:, None] - np.arange(L)[None, :], span, 64)
+    s_m = q[:, 0] @ k[:, 0].T + np.take_along_axis(c2p[:, 0], idx, 1) + np.take_along_axis(p2c[:, 0], idx, 1).T
+    s_m = s_m / np.sqrt(3 * d)
+    p = np.exp(s_m - s_m.max(1, keepdims=True)); p /= p.sum(1, keepdims=True)
+    np.testing.assert_allclose(mirrored[:, 0], p @ v[:, 0], atol=1e-12)

@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtdb_b200.so")
 
 TDB_DTYPE_F32, TDB_DTYPE_BF16 = 0, 1
-TDB_FLAG_C2P, TDB_FLAG_P2C = 1, 2
+TDB_FLAG_C2P, TDB_FLAG_P2C, TDB_FLAG_P2C_MIRRORED = 1, 2, 4
 TDB_KERNEL_AUTO, TDB_KERNEL_SIMT, TDB_KERNEL_UMMA = 0, 1, 2
 TDB_EXPAND_MARGIN = 256
 TDB_STATIC_MAX_TILES = 65535
@@ -23,7 +23,7 @@ ERR_ARG, ERR_DTYPE, ERR_ALIGN, ERR_SHAPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT
 
 EXPORTS = ["tdb_version", "tdb_strerror", "tdb_last_error", "tdb_bucket_table", "tdb_relpos_project",
            "tdb_relpos_expand", "tdb_attn_workspace_bytes", "tdb_attn_fwd_fixed", "tdb_attn_fwd_varlen",
-           "tdb_attn_fwd_varlen_static"]
+           "tdb_attn_fwd_varlen_static", "tdb_attn_fwd_fixed_scores", "tdb_attn_fwd_varlen_scores"]
 
 
 class TdbError(RuntimeError):
@@ -60,6 +60,12 @@ def _load() -> C.CDLL:
     lib.tdb_attn_fwd_varlen_static.restype = i32
     lib.tdb_attn_fwd_varlen_static.argtypes = ([vp] * 4 + [i64] * 8 + [vp, vp, i32, vp, i32, vp, vp, i32, i32]
                                                + [vp, i32, i64, i32, i32, i32, f32, i32, i32, i32, vp, vp, vp])
+    lib.tdb_attn_fwd_fixed_scores.restype = i32
+    lib.tdb_attn_fwd_fixed_scores.argtypes = ([vp] * 4 + [i64] * 12 + [vp, i64, i64, i64, vp, i64, i64, i64]
+                                              + [i32, vp, i32, vp, i32, i32, i32, i32, f32, i32, i32, vp, vp, vp])
+    lib.tdb_attn_fwd_varlen_scores.restype = i32
+    lib.tdb_attn_fwd_varlen_scores.argtypes = ([vp] * 4 + [i64] * 8 + [vp, i64, i64, vp, i64, i64]
+                                               + [i32, vp, i32, vp, i32, i64, i32, i32, i32, f32, i32, i32, vp, vp, vp])
     return lib
 
 

@@ -7,6 +7,9 @@
 // read-only cache; nothing is staged, so it is latency/L1-bound and is not the throughput path.
 //
 //   score[q,k] = (Q[q].K[k] + Q[q].Kr[r] + K[k].Qr[r]) * sm_scale,  r = idx[clamp(q-k)]
+//
+// Legacy form: the two position products arrive materialised (c2p_scores[q, r], p2c_scores[k, r]) and are only
+// gathered; with TDB_FLAG_P2C_MIRRORED the p2c term is read at idx[clamp(k-q)], the reference kernel's convention.
 #include "tdb_internal.h"
 #include <math_constants.h>
 
@@ -38,6 +41,9 @@ template <typename T> __device__ __forceinline__ T cast_out(float x);
 template <> __device__ __forceinline__ float cast_out<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 cast_out<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
 constexpr int SIMT_WARPS = 4;
 
 template <typename T>
@@ -68,8 +74,14 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_kernel(const AttnPa
   const T* qb = reinterpret_cast<const T*>(p.q) + b * p.q_sb + (tok0 + qi) * p.q_st + h * p.q_sh;
   const T* kb = reinterpret_cast<const T*>(p.k) + b * p.k_sb + tok0 * p.k_st + h * p.k_sh;
   const T* vb = reinterpret_cast<const T*>(p.v) + b * p.v_sb + tok0 * p.v_st + h * p.v_sh;
-  const T* krh = (p.flags & TDB_FLAG_C2P) ? reinterpret_cast<const T*>(p.kr) + (int64_t)h * p.two_span * 64 : nullptr;
-  const T* qrh = (p.flags & TDB_FLAG_P2C) ? reinterpret_cast<const T*>(p.qr) + (int64_t)h * p.two_span * 64 : nullptr;
+  const bool gathered = p.c2p_scores || p.p2c_scores;
+  const T* krh = (!gathered && (p.flags & TDB_FLAG_C2P)) ? reinterpret_cast<const T*>(p.kr) + (int64_t)h * p.two_span * 64 : nullptr;
+  const T* qrh = (!gathered && (p.flags & TDB_FLAG_P2C)) ? reinterpret_cast<const T*>(p.qr) + (int64_t)h * p.two_span * 64 : nullptr;
+  // materialised scores: this query's row of c2p, and the base of this head's p2c rows (one per key)
+  const T* c2p_row = ((p.flags & TDB_FLAG_C2P) && p.c2p_scores)
+      ? reinterpret_cast<const T*>(p.c2p_scores) + b * p.c2p_sb + (tok0 + qi) * p.c2p_st + h * p.c2p_sh : nullptr;
+  const T* p2c_base = ((p.flags & TDB_FLAG_P2C) && p.p2c_scores)
+      ? reinterpret_cast<const T*>(p.p2c_scores) + b * p.p2c_sb + tok0 * p.p2c_st + h * p.p2c_sh : nullptr;
 
   float qv[64], acc[64], kv[64], tv[64];
   load64<T>(qb, qv);
@@ -82,6 +94,15 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_kernel(const AttnPa
     float sc = 0.f;
 #pragma unroll
     for (int d = 0; d < 64; ++d) sc = fmaf(qv[d], kv[d], sc);
+    if (c2p_row || p2c_base) {
+      int delta = qi - kj;
+      delta = delta < -p.idx_delta_max ? -p.idx_delta_max : (delta > p.idx_delta_max ? p.idx_delta_max : delta);
+      if (c2p_row) sc += to_float(c2p_row[p.idx[delta + p.idx_delta_max]]);
+      if (p2c_base) {
+        const int r = (p.flags & TDB_FLAG_P2C_MIRRORED) ? p.idx[p.idx_delta_max - delta] : p.idx[delta + p.idx_delta_max];
+        sc += to_float(p2c_base[(int64_t)kj * p.p2c_st + r]);
+      }
+    }
     if (krh || qrh) {
       int delta = qi - kj;
       delta = delta < -p.idx_delta_max ? -p.idx_delta_max : (delta > p.idx_delta_max ? p.idx_delta_max : delta);

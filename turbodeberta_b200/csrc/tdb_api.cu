@@ -38,7 +38,8 @@ static int check_common(const AttnParams& p, int dtype, int kernel) {
   if (dtype != TDB_DTYPE_F32 && dtype != TDB_DTYPE_BF16) { set_error("dtype %d is not f32 or bf16", dtype); return TDB_ERR_DTYPE; }
   if (p.D != 64) { set_error("head_dim %d: only 64 is supported", p.D); return TDB_ERR_SHAPE; }
   if (p.H <= 0 || p.n_seqs < 0 || p.L < 0) { set_error("negative or zero size (H=%d, n_seqs=%d, L=%d)", p.H, p.n_seqs, p.L); return TDB_ERR_ARG; }
-  if (p.flags & ~(TDB_FLAG_C2P | TDB_FLAG_P2C)) { set_error("unknown flag bits 0x%x", p.flags); return TDB_ERR_ARG; }
+  const bool gathered = p.c2p_scores || p.p2c_scores;
+  if (p.flags & ~(TDB_FLAG_C2P | TDB_FLAG_P2C | (gathered ? TDB_FLAG_P2C_MIRRORED : 0))) { set_error("unknown flag bits 0x%x", p.flags); return TDB_ERR_ARG; }
   if (kernel < TDB_KERNEL_AUTO || kernel > TDB_KERNEL_UMMA) { set_error("unknown kernel selector %d", kernel); return TDB_ERR_ARG; }
   if (!(p.sm_scale > 0.f) || !(p.sm_scale < 1e6f)) { set_error("sm_scale must be a positive finite number"); return TDB_ERR_ARG; }
   if (!p.status) { set_error("status word pointer is null"); return TDB_ERR_ARG; }
@@ -50,8 +51,17 @@ static int check_common(const AttnParams& p, int dtype, int kernel) {
   if (p.flags) {
     if (p.two_span <= 0 || p.two_span > 32767) { set_error("two_span %d out of range", p.two_span); return TDB_ERR_SHAPE; }
     if (!p.idx || p.idx_delta_max <= 0) { set_error("position terms requested without an index table"); return TDB_ERR_ARG; }
-    if ((p.flags & TDB_FLAG_C2P) && (!p.kr || !aligned16(p.kr))) { set_error("kr table missing or misaligned"); return p.kr ? TDB_ERR_ALIGN : TDB_ERR_ARG; }
-    if ((p.flags & TDB_FLAG_P2C) && (!p.qr || !aligned16(p.qr))) { set_error("qr table missing or misaligned"); return p.qr ? TDB_ERR_ALIGN : TDB_ERR_ARG; }
+    if (gathered) {
+      if ((p.flags & TDB_FLAG_C2P) && !p.c2p_scores) { set_error("c2p requested without c2p_scores"); return TDB_ERR_ARG; }
+      if ((p.flags & TDB_FLAG_P2C) && !p.p2c_scores) { set_error("p2c requested without p2c_scores"); return TDB_ERR_ARG; }
+      if (((p.flags & TDB_FLAG_C2P) && (p.c2p_st <= 0 || p.c2p_sh <= 0 || p.c2p_sb < 0)) ||
+          ((p.flags & TDB_FLAG_P2C) && (p.p2c_st <= 0 || p.p2c_sh <= 0 || p.p2c_sb < 0))) {
+        set_error("position score tensor has a non-positive stride"); return TDB_ERR_ARG;
+      }
+    } else {
+      if ((p.flags & TDB_FLAG_C2P) && (!p.kr || !aligned16(p.kr))) { set_error("kr table missing or misaligned"); return p.kr ? TDB_ERR_ALIGN : TDB_ERR_ARG; }
+      if ((p.flags & TDB_FLAG_P2C) && (!p.qr || !aligned16(p.qr))) { set_error("qr table missing or misaligned"); return p.qr ? TDB_ERR_ALIGN : TDB_ERR_ARG; }
+    }
   }
   return TDB_OK;
 }
@@ -206,6 +216,65 @@ TDB_API int tdb_attn_fwd_varlen(const void* q, const void* k, const void* v, voi
     return TDB_ERR_WORKSPACE;
   }
   return launch_attn_umma(p, (cudaStream_t)stream);
+}
+
+TDB_API int tdb_attn_fwd_fixed_scores(const void* q, const void* k, const void* v, void* o,
+                        int64_t q_sb, int64_t q_st, int64_t q_sh, int64_t k_sb, int64_t k_st, int64_t k_sh,
+                        int64_t v_sb, int64_t v_st, int64_t v_sh, int64_t o_sb, int64_t o_st, int64_t o_sh,
+                        const void* c2p_scores, int64_t c2p_sb, int64_t c2p_st, int64_t c2p_sh,
+                        const void* p2c_scores, int64_t p2c_sb, int64_t p2c_st, int64_t p2c_sh,
+                        int two_span, const int16_t* idx, int idx_delta_max,
+                        const int32_t* seqlens, int B, int L, int H, int D, float sm_scale, int flags, int dtype,
+                        float* lse, int32_t* status, void* stream) {
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = q; p.k = k; p.v = v; p.o = o;
+  p.q_sb = q_sb; p.q_st = q_st; p.q_sh = q_sh; p.k_sb = k_sb; p.k_st = k_st; p.k_sh = k_sh;
+  p.v_sb = v_sb; p.v_st = v_st; p.v_sh = v_sh; p.o_sb = o_sb; p.o_st = o_st; p.o_sh = o_sh;
+  p.c2p_scores = c2p_scores; p.c2p_sb = c2p_sb; p.c2p_st = c2p_st; p.c2p_sh = c2p_sh;
+  p.p2c_scores = p2c_scores; p.p2c_sb = p2c_sb; p.p2c_st = p2c_st; p.p2c_sh = p2c_sh;
+  p.two_span = two_span; p.idx = idx; p.idx_delta_max = idx_delta_max;
+  p.seqlens = seqlens; p.varlen = 0; p.n_seqs = B; p.L = L; p.total_tokens = (int64_t)B * L;
+  p.H = H; p.D = D; p.sm_scale = sm_scale; p.flags = flags;
+  p.lse = lse; p.lse_sb = (int64_t)H * L; p.lse_sh = L; p.status = status;
+  if (B < 0 || L < 0) { set_error("negative size"); return TDB_ERR_ARG; }
+  if (B == 0 || L == 0) return TDB_OK;
+  if (!c2p_scores && !p2c_scores) { set_error("no position scores given: use tdb_attn_fwd_fixed"); return TDB_ERR_ARG; }
+  int rc = check_common(p, dtype, TDB_KERNEL_SIMT);
+  if (rc) return rc;
+  if (B > 1 && (q_sb <= 0 || k_sb <= 0 || v_sb <= 0 || o_sb <= 0)) { set_error("batch stride must be positive when B > 1"); return TDB_ERR_ARG; }
+  return launch_attn_simt(p, dtype, (cudaStream_t)stream);
+}
+
+TDB_API int tdb_attn_fwd_varlen_scores(const void* q, const void* k, const void* v, void* o,
+                        int64_t q_st, int64_t q_sh, int64_t k_st, int64_t k_sh, int64_t v_st, int64_t v_sh,
+                        int64_t o_st, int64_t o_sh,
+                        const void* c2p_scores, int64_t c2p_st, int64_t c2p_sh,
+                        const void* p2c_scores, int64_t p2c_st, int64_t p2c_sh,
+                        int two_span, const int16_t* idx, int idx_delta_max,
+                        const int32_t* cu_seqlens, int n_seqs, int64_t total_tokens, int max_seqlen,
+                        int H, int D, float sm_scale, int flags, int dtype,
+                        float* lse, int32_t* status, void* stream) {
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = q; p.k = k; p.v = v; p.o = o;
+  p.q_st = q_st; p.q_sh = q_sh; p.k_st = k_st; p.k_sh = k_sh; p.v_st = v_st; p.v_sh = v_sh; p.o_st = o_st; p.o_sh = o_sh;
+  p.c2p_scores = c2p_scores; p.c2p_st = c2p_st; p.c2p_sh = c2p_sh;
+  p.p2c_scores = p2c_scores; p.p2c_st = p2c_st; p.p2c_sh = p2c_sh;
+  p.two_span = two_span; p.idx = idx; p.idx_delta_max = idx_delta_max;
+  p.cu_seqlens = cu_seqlens; p.varlen = 1; p.n_seqs = n_seqs; p.L = max_seqlen; p.total_tokens = total_tokens;
+  p.H = H; p.D = D; p.sm_scale = sm_scale; p.flags = flags;
+  p.lse = lse; p.lse_sb = 0; p.lse_sh = total_tokens; p.status = status;
+  if (n_seqs == 0 || total_tokens == 0) {
+    if (n_seqs < 0 || total_tokens < 0) { set_error("negative size"); return TDB_ERR_ARG; }
+    return TDB_OK;
+  }
+  if (!cu_seqlens) { set_error("cu_seqlens is null"); return TDB_ERR_ARG; }
+  if (max_seqlen <= 0 || max_seqlen > total_tokens) { set_error("max_seqlen %d outside [1, total_tokens]", max_seqlen); return TDB_ERR_ARG; }
+  if (!c2p_scores && !p2c_scores) { set_error("no position scores given: use tdb_attn_fwd_varlen"); return TDB_ERR_ARG; }
+  int rc = check_common(p, dtype, TDB_KERNEL_SIMT);
+  if (rc) return rc;
+  return launch_attn_simt(p, dtype, (cudaStream_t)stream);
 }
 
 // Same as tdb_attn_fwd_varlen, with the tile list kept in the library's fixed device array instead of a

@@ -20,6 +20,10 @@ struct AttnParams {
   const void* kr; const void* qr; int two_span;          // [H, two_span, D] of the I/O dtype
   const int16_t* idx; int idx_delta_max;                  // delta -> table row
   const void* kr_exp; const void* qr_exp;                 // [H, exp_rows, D] bf16, row x <-> delta = x - exp_delta_max
+  // Materialised position scores (legacy op interface): c2p_scores[b, h, t, r] = Q[t].Kr[r], p2c_scores[b, h, t, r]
+  // = K[t].Qr[r], rows of two_span contiguous elements of the I/O dtype.  When set they replace kr / qr.
+  const void* c2p_scores; const void* p2c_scores;
+  int64_t c2p_sb, c2p_st, c2p_sh, p2c_sb, p2c_st, p2c_sh;
   int exp_delta_max, exp_rows;
   const int32_t* seqlens;                                 // padded form, may be null
   const int32_t* cu_seqlens;                              // packed form

@@ -10,6 +10,8 @@ q, k, v are ``(T, H, D)`` with the sequences back to back; ``cu_seqlens`` is int
 fixed-length op, ``q_pos``/``k_pos`` are the projected tables ``(H, 2*span, D)`` rather than the per-token score
 tensors ``(T, H, 2*span)`` of the reference.  Relative positions restart at every sequence.  The tile list is
 built on the device from ``cu_seqlens``; nothing is read back except the status words at the end of the call.
+Score tensors of shape ``(T, H, 2*span)`` are still accepted and gathered by a CUDA-core compatibility kernel
+(``p2c_mirrored=True`` reproduces the reference kernel's index, ``ops/flash_attention_varlen.py:144-152``).
 """
 from __future__ import annotations
 
@@ -18,7 +20,8 @@ import math
 import torch
 
 from .. import _cabi as cabi
-from .flash_attention import _PENDING_STATUS, _check_status, _tables_from_args
+from .flash_attention import (_PENDING_STATUS, _check_status, _index_table_for_scores, _is_materialised,
+                              _tables_from_args)
 
 
 class _VarlenFn(torch.autograd.Function):
@@ -76,10 +79,56 @@ class _VarlenFn(torch.autograd.Function):
         raise RuntimeError("turbodeberta_b200 attention is forward-only (as in the reference: no backward kernel)")
 
 
+def _scores_varlen(q, k, v, c2p_scores, p2c_scores, cu_seqlens, max_seqlen, sm_scale, position_buckets,
+                   max_relative_distance, p2c_mirrored, return_lse, check_status):
+    """Legacy form of the packed op: gather from materialised ``(T, H, 2*span)`` score tensors."""
+    dev = cabi.require_cuda(q, k, v, cu_seqlens)
+    if q.dim() != 3 or k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("q, k, v must share the shape (T, H, D)")
+    T, H, D = q.shape
+    code = cabi.dtype_code(q.dtype)
+    some = c2p_scores if c2p_scores is not None else p2c_scores
+    two_span = some.shape[-1]
+    for t, name in ((c2p_scores, "q_pos"), (p2c_scores, "k_pos")):
+        if t is not None and (tuple(t.shape) != (T, H, two_span) or t.dtype != q.dtype or t.stride(-1) != 1):
+            raise ValueError(f"{name} must be (T, H, 2*span) of q's dtype with a contiguous last dimension")
+    for t in (q, k, v):
+        if t.stride(-1) != 1:
+            raise ValueError("the head dimension must be contiguous")
+    if cu_seqlens.dtype != torch.int32 or cu_seqlens.dim() != 1 or cu_seqlens.numel() < 1:
+        raise ValueError("cu_seqlens must be a 1-D int32 tensor of n_seqs + 1 offsets")
+    cu_seqlens = cu_seqlens.contiguous()
+    n_seqs = cu_seqlens.numel() - 1
+    idx, idm = _index_table_for_scores(two_span, position_buckets, max_relative_distance, dev)
+    o = torch.empty((T, H, D), dtype=q.dtype, device=dev)
+    lse = torch.empty((H, T), dtype=torch.float32, device=dev) if return_lse else None
+    if T == 0 or n_seqs == 0:
+        return o, lse
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    flags = ((cabi.TDB_FLAG_C2P if c2p_scores is not None else 0) | (cabi.TDB_FLAG_P2C if p2c_scores is not None else 0)
+             | (cabi.TDB_FLAG_P2C_MIRRORED if p2c_mirrored else 0))
+
+    def s(t):
+        return (t.stride(0), t.stride(1)) if t is not None else (0, 0)
+
+    with torch.cuda.device(dev):
+        rc = cabi.lib.tdb_attn_fwd_varlen_scores(
+            cabi.ptr(q), cabi.ptr(k), cabi.ptr(v), cabi.ptr(o), *s(q), *s(k), *s(v), *s(o),
+            cabi.ptr(c2p_scores), *s(c2p_scores), cabi.ptr(p2c_scores), *s(p2c_scores), two_span, cabi.ptr(idx), idm,
+            cabi.ptr(cu_seqlens), n_seqs, T, max_seqlen, H, D, float(sm_scale), flags, code, cabi.ptr(lse),
+            cabi.ptr(status), cabi.stream_ptr(dev))
+    cabi.check(rc)
+    if check_status:
+        _check_status(status)
+    else:
+        _PENDING_STATUS.append(status)
+    return o, lse
+
+
 def flash_attention_with_disentangled_varlen(q, k, v, q_pos, k_pos, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
                                              max_seqlen_k, causal=False, sm_scale=None, position_buckets=0,
                                              max_relative_distance=0, *, tables=None, kernel=cabi.TDB_KERNEL_AUTO,
-                                             return_lse=False, check_status=True):
+                                             return_lse=False, check_status=True, p2c_mirrored=False):
     """Fused disentangled attention on packed ``(T, H, D)`` inputs; returns ``o`` of the same shape."""
     if causal:
         raise NotImplementedError("causal masking is not part of the DeBERTa encoder path")
@@ -91,6 +140,15 @@ def flash_attention_with_disentangled_varlen(q, k, v, q_pos, k_pos, cu_seqlens_q
     T = q.shape[0]
     max_seqlen = max(int(max_seqlen_q), int(max_seqlen_k if max_seqlen_k is not None else max_seqlen_q))
     max_seqlen = max(1, min(max_seqlen, T)) if T > 0 else 1
+    mat = lambda t: _is_materialised(t, q, position_buckets, max_relative_distance)
+    if tables is None and (mat(q_pos) or mat(k_pos)):
+        if (q_pos is not None and not mat(q_pos)) or (k_pos is not None and not mat(k_pos)):
+            raise ValueError("q_pos and k_pos must both be tables (H, 2*span, D) or both be score tensors (T, H, 2*span)")
+        o, lse = _scores_varlen(q, k, v, q_pos, k_pos, cu_seqlens_q, max_seqlen, sm_scale, position_buckets,
+                                max_relative_distance, p2c_mirrored, return_lse, check_status)
+        return (o, lse) if return_lse else o
+    if p2c_mirrored:
+        raise ValueError("p2c_mirrored applies to materialised score tensors only")
     tables = _tables_from_args(q_pos, k_pos, q, position_buckets, max_relative_distance, tables)
     o, lse, status = _VarlenFn.apply(q, k, v, tables, cu_seqlens_q, max_seqlen, sm_scale, kernel, return_lse,
                                      check_status)
