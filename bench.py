@@ -291,28 +291,44 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The clock sampler is started (and given its second to produce a first sample) BEFORE the warm-up steps, so that
+    # the timed region follows the warm-up without an idle gap in which the GPU would drop its clocks.
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(1.5)            # nvidia-smi needs about a second before its first sample
     for _ in range(max(3, args.warmup)):
         flush.zero_()
         o = step()
     torch.cuda.synchronize()
     # sanity: the output of the timed call is finite on valid rows
     assert torch.isfinite(o.float()).all(), "attention output is not finite"
+    def timed_loop():
+        barrier()
+        t_begin = time.time()
+        evs = []
+        for _ in range(args.steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); step(); e1.record()
+            evs.append((e0, e1))
+        barrier()
+        return t_begin, time.time(), [a.elapsed_time(b) for a, b in evs]
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
-        time.sleep(1.5)            # nvidia-smi needs about a second before its first sample
-    barrier()
-    w0 = time.time()
-    evs = []
-    for _ in range(args.steps):
-        flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(); step(); e1.record()
-        evs.append((e0, e1))
-    barrier()
-    w1 = time.time()
-    times = [a.elapsed_time(b) for a, b in evs]
+    # A shared host can stall the GPU for milliseconds (another tenant's management query, a context switch): a single
+    # step then takes tens of times the median and skews the K-step total.  Such a region is measured again, once, in
+    # full; the first attempt is reported beside the result.
+    w0, w1, times = timed_loop()
+    remeasured = None
+    med = sorted(times)[len(times) // 2]
+    disturbed = torch.tensor([1.0 if (len(times) >= 20 and max(times) > 8.0 * med) else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(disturbed, op=dist.ReduceOp.MAX)
+    if disturbed.item() > 0:
+        remeasured = {"first_attempt_ms_per_step": float(sum(times)) / args.steps, "first_attempt_slowest_step_ms": max(times),
+                      "first_attempt_median_step_ms": med,
+                      "reason": "one step of the first attempt took more than 8x the median step (external stall)"}
+        w0, w1, times = timed_loop()
     total_ms = float(sum(times))
     clocks = None
     if sampler:
@@ -470,6 +486,8 @@ def run_ours(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if remeasured is not None:
+            line["remeasured"] = remeasured
         if e2e_ms is not None:
             line["e2e"] = {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_max,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "call": e2e_api,
@@ -534,14 +552,13 @@ def run_encoder(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:                                   # before the warm-up: no idle gap between warm-up and timed region
+        sampler.start(); time.sleep(1.5)
     for _ in range(max(3, args.warmup)):
         out = step()
     barrier()
     assert torch.isfinite(out.float()).all()
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start(); time.sleep(1.5)
-    barrier()
     w0 = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
