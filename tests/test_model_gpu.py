@@ -139,3 +139,36 @@ def test_packed_encoder_route_matches_padded_route(dtype):
         assert (a[v] - b_[v]).abs().max().item() / scale < tol
     assert torch.count_nonzero(packed.last_hidden_state.float().cpu()[~v]).item() == 0
     assert torch.equal(packed.last_hidden_state, packed.hidden_states[-1])
+
+
+def test_encoder_forward_captures_into_a_cuda_graph():
+    """After a warm-up with the same mask tensor (tables, fused weights and the mask analysis are cached) the whole
+    model forward records into a CUDA graph: no allocation in the library, no synchronisation on the path; the
+    replay reproduces the eager forward bit for bit and leaves the status words for the next check."""
+    from turbodeberta_b200.model import FlashDebertaV2Model
+    from turbodeberta_b200.ops.flash_attention import check_pending_status
+    torch.manual_seed(9)
+    model = FlashDebertaV2Model(_cfg(num_hidden_layers=3)).eval().cuda().to(torch.bfloat16)
+    ids = torch.randint(0, 500, (4, 256), device="cuda")
+    mask = torch.ones_like(ids)
+
+    @torch.no_grad()
+    def fwd():
+        return model(input_ids=ids, attention_mask=mask).last_hidden_state
+
+    eager = fwd().clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fwd()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fwd()
+    ids.copy_(torch.randint(0, 500, (4, 256), device="cuda"))        # new contents in the captured input buffer
+    graph.replay()
+    torch.cuda.synchronize()
+    check_pending_status()                                           # the replay's status words are readable now
+    fresh = fwd()
+    assert torch.equal(out, fresh)
+    assert not torch.equal(out, eager)

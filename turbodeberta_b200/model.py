@@ -52,6 +52,18 @@ class MaskInfo:
 _MASK_CACHE: dict = {}
 
 
+def _mask_cache_put(tensor: torch.Tensor, info) -> None:
+    """Remember the analysis of a live mask tensor.  Entries of tensors that have been freed are dropped first; only
+    if more than 64 live masks are tracked does the oldest entry go (so a mask that is passed again and again, e.g.
+    the static input of a captured graph, is never re-analysed because other masks came and went)."""
+    dead = [k for k, (ref, _, _) in _MASK_CACHE.items() if ref() is None]
+    for k in dead:
+        del _MASK_CACHE[k]
+    while len(_MASK_CACHE) >= 64:
+        del _MASK_CACHE[next(iter(_MASK_CACHE))]
+    _MASK_CACHE[id(tensor)] = (weakref.ref(tensor), tensor._version, info)
+
+
 def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int) -> MaskInfo:
     """Reduce a ``[B,L]``, ``[B,L,L]`` or ``[B,1,L,L]`` mask to per-row key validity.
 
@@ -90,9 +102,7 @@ def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int) -
     prefix = torch.arange(length, device=key_mask.device)[None, :] < seqlens[:, None]
     flags = torch.stack([key_mask.all(), (prefix == key_mask).all()]).tolist()      # the one sync
     info = MaskInfo(bool(flags[0]), bool(flags[1]), seqlens, key_mask)
-    if len(_MASK_CACHE) > 8:
-        _MASK_CACHE.clear()
-    _MASK_CACHE[key] = (weakref.ref(attention_mask), attention_mask._version, info)
+    _mask_cache_put(attention_mask, info)
     return info
 
 
@@ -232,18 +242,38 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
 
     def forward(self, hidden_states, attention_mask, output_hidden_states=True, output_attentions=False,
                 query_states=None, relative_pos=None, return_dict=True):
-        if (self.pack_padded_batches and query_states is None and self.conv is None and not output_attentions
+        self._mask_info = None
+        if (query_states is None and self.conv is None and not output_attentions
                 and hidden_states.is_cuda and hidden_states.dim() == 3):
+            # One analysis of the user's mask per forward (cached per mask tensor, so a repeated call with the same
+            # tensor - e.g. while the forward is being captured into a CUDA graph - costs no synchronisation); the
+            # expanded mask that the HF encoder builds from it inherits the result in get_attention_mask().
             info = analyse_mask(attention_mask, hidden_states.shape[0], hidden_states.shape[1])
-            if not info.all_ones:
+            if self.pack_padded_batches and not info.all_ones:
                 out = self._forward_packed(hidden_states, info, output_hidden_states, return_dict)
-                check_pending_status()
+                self._check_status_unless_capturing()
                 return out
+            self._mask_info = info
         out = super().forward(hidden_states, attention_mask, output_hidden_states=output_hidden_states,
                               output_attentions=output_attentions, query_states=query_states,
                               relative_pos=relative_pos, return_dict=return_dict)
-        check_pending_status()          # one synchronisation per encoder forward instead of one per layer
+        self._check_status_unless_capturing()   # one synchronisation per encoder forward instead of one per layer
         return out
+
+    def get_attention_mask(self, attention_mask):
+        out = super().get_attention_mask(attention_mask)
+        info = getattr(self, "_mask_info", None)
+        if info is not None and isinstance(out, torch.Tensor) and out is not attention_mask:
+            _mask_cache_put(out, info)
+        return out
+
+    @staticmethod
+    def _check_status_unless_capturing():
+        """Reading the device status words synchronises, which a stream capture does not allow: while the forward is
+        being captured into a CUDA graph the words stay pending (the graph's replays rewrite them) and the next
+        ``check_pending_status()`` outside a capture reads them."""
+        if not torch.cuda.is_current_stream_capturing():
+            check_pending_status()
 
     def _forward_packed(self, hidden_states, info: MaskInfo, output_hidden_states: bool, return_dict: bool):
         """The layer loop of the HF encoder (``modeling_deberta_v2.py:630-682``) on valid tokens only.  The reference
