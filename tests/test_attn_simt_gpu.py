@@ -73,8 +73,11 @@ def test_argument_errors():
         flash_attention_with_disentangled(q, q, q, None, None)                  # fp16
     q = torch.zeros(1, 2, 16, 64, device="cuda")
     with pytest.raises(ValueError):
-        flash_attention_with_disentangled(q, q, q, torch.zeros(1, 2, 16, 512, device="cuda"), None,
+        flash_attention_with_disentangled(q, q, q, torch.zeros(1, 2, 16, 300, device="cuda"), None,
+                                          position_buckets=256, max_relative_distance=512)   # 300 columns are neither
+    o = flash_attention_with_disentangled(q, q, q, torch.zeros(1, 2, 16, 512, device="cuda"), None,
                                           position_buckets=256, max_relative_distance=512)   # materialised scores
+    assert o.shape == q.shape and torch.isfinite(o).all()
     with pytest.raises(RuntimeError):
         flash_attention_with_disentangled(q.cpu(), q.cpu(), q.cpu(), None, None)            # no CPU path
     with pytest.raises(NotImplementedError):
