@@ -30,7 +30,9 @@ METRIC = "disentangled_attn_algorithmic_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on the default workload,
 # from the ncu capture summarised in profiles/attn_umma_config2.md.
-NCU_TRAFFIC_BYTES = 61.16e6     # profiles/attn_umma_config2.md: 56.32 MB read + 4.6..5.1 MB written per launch
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu captures summarised in
+# profiles/attn_umma_config2.md (56.32 MB read + 4.6..5.1 MB written) and profiles/attn_umma_config3.md.
+NCU_TRAFFIC_BYTES = {"c2": 61.16e6, "c3": 525.5e6}
 
 
 def parse():
@@ -524,7 +526,7 @@ def run_ours(args):
                        "l2": "256 MiB buffer rewritten between timed steps", "parallelism": f"replicas x{world} (the same seeded batch on every rank)",
                        "launch": launch_mode},
             "roofline": {"bound": "tensor", "achieved": kern_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": kern_tflops / pk["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,
+                         "frac": kern_tflops / pk["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "peak_source": pk["source"] + " (burst)", "algorithmic_flops_per_launch": flops,
                          "algorithmic_bytes_per_launch": bytes_alg,
                          "hbm_floor_ms": bytes_alg / (pk["hbm_gbs"] * 1e9) * 1e3},
