@@ -141,10 +141,16 @@ __global__ void __launch_bounds__(1024) build_tile_list_kernel(const int32_t* __
   }
 }
 
-__device__ __forceinline__ float lds_bf16(uint32_t addr) {
+// x + (a bf16 value in a 16-bit register): the conversion rides on the add.
+__device__ __forceinline__ float add_bf16(float x, uint16_t h) {
+  float y;
+  asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(y) : "h"(h), "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint16_t lds_u16(uint32_t addr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return __uint_as_float(((uint32_t)v) << 16);
+  return v;
 }
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
   uint32_t v;
@@ -739,8 +745,10 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
 #pragma unroll
             for (int k = 0; k < KPT / 2; ++k) {
               const uint32_t v = __funnelshift_r(wv[k], wv[k + 1], sh);       // (element 2k, element 2k+1) ascending
-              s[KPT - 1 - 2 * k] += __uint_as_float(v << 16);
-              s[KPT - 2 - 2 * k] += __uint_as_float(v & 0xffff0000u);
+              uint16_t lo, hi;
+              asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(v));
+              s[KPT - 1 - 2 * k] = add_bf16(s[KPT - 1 - 2 * k], lo);
+              s[KPT - 2 - 2 * k] = add_bf16(s[KPT - 2 - 2 * k], hi);
             }
           }
           TL0(11500 + g);
@@ -781,8 +789,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           for (int e = 0; e < KPT; e += 2) {
             float x0 = s[e], x1 = s[e + 1];
             if (P2C) {
-              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * (e & 31)));
-              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31)));
+              x0 = add_bf16(x0, lds_u16(p_read + (uint32_t)(e * STG_STRIDE - 2 * (e & 31))));
+              x1 = add_bf16(x1, lds_u16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31))));
             }
             s[e] = x0; s[e + 1] = x1;
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
@@ -794,8 +802,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           for (int e = 0; e < KPT; e += 2) {
             float x0 = s[e], x1 = s[e + 1];
             if (P2C) {
-              x0 += lds_bf16(p_read + (uint32_t)(e * STG_STRIDE - 2 * (e & 31)));
-              x1 += lds_bf16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31)));
+              x0 = add_bf16(x0, lds_u16(p_read + (uint32_t)(e * STG_STRIDE - 2 * (e & 31))));
+              x1 = add_bf16(x1, lds_u16(p_read + (uint32_t)((e + 1) * STG_STRIDE - 2 * ((e + 1) & 31))));
             }
             x0 = (e < nvalid) ? x0 : -CUDART_INF_F;                      // keys beyond the sequence end
             x1 = (e + 1 < nvalid) ? x1 : -CUDART_INF_F;
