@@ -31,8 +31,8 @@ UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on the default workload,
 # from the ncu capture summarised in profiles/attn_umma_config2.md.
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu captures summarised in
-# profiles/attn_umma_config2.md (56.32 MB read + 4.6..5.1 MB written) and profiles/attn_umma_config3.md.
-NCU_TRAFFIC_BYTES = {"c2": 61.16e6, "c3": 525.5e6}
+# profiles/attn_umma_config2.md (56.31 MB read + 4.9..5.1 MB written) and profiles/attn_umma_config3.md.
+NCU_TRAFFIC_BYTES = {"c2": 61.30e6, "c3": 525.5e6}
 
 
 def parse():
