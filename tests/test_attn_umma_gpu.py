@@ -189,3 +189,32 @@ def test_umma_reference_exponent_moves(mode):
                                            None, None, False, scale, 256, 512, seqlens=lens, tables=tables, kernel=SIMT)
     assert (o.float() - o2.float()).abs().max().item() < 2e-2
     assert torch.isfinite(lse).all()
+
+
+def test_umma_many_single_tile_items():
+    """Thousands of short sequences: every work item is one key tile, so each tile of the stream is an item's first
+    and last at once (deferred epilogue, item hand-over and work ring all turn over at every step)."""
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+    rng = np.random.default_rng(123)
+    lengths = rng.integers(1, 41, 3000)
+    lengths[::97] = 0                                   # some empty sequences in between
+    lengths[5] = 128; lengths[6] = 129                   # and a few that are exactly one tile / just over
+    w = workloads.make_attention_workload("tiny", seed=124, hidden_size=128, num_heads=2, lengths=lengths,
+                                          padded_len=None, dtype=DT)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    cu = torch.as_tensor(np.asarray(w.cu_seqlens), dtype=torch.int32, device="cuda")
+    scale = 1.0 / (3 * 64) ** 0.5
+    mx = int(lengths.max())
+    o = flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, mx, mx, False, scale, 256, 512,
+                                                 tables=tables, kernel=UMMA)
+    o2 = flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, mx, mx, False, scale, 256, 512,
+                                                  tables=tables, kernel=SIMT)
+    assert torch.isfinite(o.float()).all()
+    assert (o.float() - o2.float()).abs().max().item() < 1e-2
+    cuh = np.asarray(w.cu_seqlens)
+    for b in (0, 5, 6, 1500, 2999):                      # and against the oracle on a few of them
+        s, e = int(cuh[b]), int(cuh[b + 1])
+        if e > s:
+            ref = util.oracle_varlen(q[s:e], k[s:e], v[s:e], tables, np.array([0, e - s]), w, sm_scale=scale)
+            util.assert_close(o[s:e], ref, DT, f"tiny sequence {b}")
