@@ -156,6 +156,12 @@ TDB_API int tdb_attn_fwd_varlen_static(const void* q, const void* k, const void*
                         int H, int D, float sm_scale, int flags, int dtype, int kernel,
                         float* lse, int32_t* status, void* stream);
 
+/* Diagnostic (no counterpart in the reference): launches one warp that waits, with the same bounded wait every hand-off
+ * of the tensor-core kernels uses, on a barrier that nothing completes.  After at most limit_us microseconds (1..100000)
+ * the wait gives up and writes `code` (> 0) into status[0]; the kernel then returns normally and the context stays
+ * usable.  Lets a caller check, without any fault, that a stuck hand-off would be reported rather than hang. */
+TDB_API int tdb_selftest_bounded_wait(int32_t* status, int code, int limit_us, void* stream);
+
 /* Legacy operator form (reference ops/flash_attention.py:345-369 and ops/flash_attention_varlen.py:348-374 called with
  * the MATERIALISED position scores of model.py:122-125 / 143-148): c2p_scores[b, h, t, r] = Q[t].Kr[r] and
  * p2c_scores[b, h, t, r] = K[t].Qr[r] (rows of two_span contiguous elements of the I/O dtype; either may be null with

@@ -23,7 +23,8 @@ ERR_ARG, ERR_DTYPE, ERR_ALIGN, ERR_SHAPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT
 
 EXPORTS = ["tdb_version", "tdb_strerror", "tdb_last_error", "tdb_bucket_table", "tdb_relpos_project",
            "tdb_relpos_expand", "tdb_attn_workspace_bytes", "tdb_attn_fwd_fixed", "tdb_attn_fwd_varlen",
-           "tdb_attn_fwd_varlen_static", "tdb_attn_fwd_fixed_scores", "tdb_attn_fwd_varlen_scores"]
+           "tdb_attn_fwd_varlen_static", "tdb_attn_fwd_fixed_scores", "tdb_attn_fwd_varlen_scores",
+           "tdb_selftest_bounded_wait"]
 
 
 class TdbError(RuntimeError):
@@ -60,6 +61,8 @@ def _load() -> C.CDLL:
     lib.tdb_attn_fwd_varlen_static.restype = i32
     lib.tdb_attn_fwd_varlen_static.argtypes = ([vp] * 4 + [i64] * 8 + [vp, vp, i32, vp, i32, vp, vp, i32, i32]
                                                + [vp, i32, i64, i32, i32, i32, f32, i32, i32, i32, vp, vp, vp])
+    lib.tdb_selftest_bounded_wait.restype = i32
+    lib.tdb_selftest_bounded_wait.argtypes = [vp, i32, i32, vp]
     lib.tdb_attn_fwd_fixed_scores.restype = i32
     lib.tdb_attn_fwd_fixed_scores.argtypes = ([vp] * 4 + [i64] * 12 + [vp, i64, i64, i64, vp, i64, i64, i64]
                                               + [i32, vp, i32, vp, i32, i32, i32, i32, f32, i32, i32, vp, vp, vp])

@@ -123,6 +123,23 @@ relpos_project_umma_kernel(const __grid_constant__ CUtensorMap tm_rel, const __g
   if (warp == 5) tmem_dealloc(tmem, 64);
 }
 
+// Self-test of the bounded wait that every hand-off of the tensor-core kernels goes through: one warp waits on an
+// mbarrier that nothing will ever complete.  The wait must give up after `limit_ns`, set the abort flag, record
+// `code` in the status word and return, leaving the context usable.
+__global__ void __launch_bounds__(32, 1) bounded_wait_selftest_kernel(int32_t* status, int code, uint64_t limit_ns) {
+  __shared__ __align__(8) uint64_t barrier_word;
+  __shared__ int abort_word;
+  const uint32_t b = smem_u32(&barrier_word);
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(b, 1u);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  const bool done = mbar_wait(b, 0u, &abort_word, status, code, limit_ns);
+  if (done && threadIdx.x == 0) atomicExch(status + 3, 1);     // cannot happen: nobody arrives
+}
+
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   if (!fn) {
@@ -175,6 +192,11 @@ int launch_relpos_project_umma(const void* rel, const void* W, const void* bias,
   relpos_project_umma_kernel<<<grid, P_THREADS, P_SMEM, s>>>(tm_rel, tm_w, (const __nv_bfloat16*)bias, two_span, hidden, H,
                                                              (__nv_bfloat16*)out, status);
   return cuda_fail(cudaGetLastError(), "relpos_project_umma launch");
+}
+
+int launch_bounded_wait_selftest(int32_t* status, int code, uint64_t limit_ns, cudaStream_t s) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, s>>>(status, code, limit_ns);
+  return cuda_fail(cudaGetLastError(), "bounded-wait self-test launch");
 }
 
 }  // namespace tdb

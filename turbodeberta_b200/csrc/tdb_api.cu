@@ -149,6 +149,13 @@ TDB_API int tdb_relpos_expand(const void* table, const int16_t* idx, int idx_del
                               (cudaStream_t)stream);
 }
 
+TDB_API int tdb_selftest_bounded_wait(int32_t* status, int code, int limit_us, void* stream) {
+  if (!status) { set_error("status word pointer is null"); return TDB_ERR_ARG; }
+  if (code <= 0) { set_error("code must be positive"); return TDB_ERR_ARG; }
+  if (limit_us <= 0 || limit_us > 100000) { set_error("limit of %d us outside (0, 100000]", limit_us); return TDB_ERR_ARG; }
+  return launch_bounded_wait_selftest(status, code, (uint64_t)limit_us * 1000ull, (cudaStream_t)stream);
+}
+
 TDB_API size_t tdb_attn_workspace_bytes(int n_seqs, int64_t total_tokens) {
   if (n_seqs < 0 || total_tokens < 0) return 0;
   return umma_workspace_bytes(n_seqs, total_tokens);

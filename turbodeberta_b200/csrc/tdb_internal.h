@@ -50,6 +50,7 @@ int launch_relpos_project_umma(const void* rel, const void* W, const void* bias,
                                void* out, int32_t* status, cudaStream_t s);
 int launch_relpos_expand(const void* table, const int16_t* idx, int idx_delta_max, int H, int two_span, int D,
                          int dtype, int exp_delta_max, int exp_rows, void* out, cudaStream_t s);
+int launch_bounded_wait_selftest(int32_t* status, int code, uint64_t limit_ns, cudaStream_t s);
 int launch_attn_simt(const AttnParams& p, int dtype, cudaStream_t s);
 int launch_attn_umma(const AttnParams& p, cudaStream_t s);
 size_t umma_workspace_bytes(int n_seqs, int64_t total_tokens);
