@@ -218,3 +218,18 @@ def test_umma_many_single_tile_items():
         if e > s:
             ref = util.oracle_varlen(q[s:e], k[s:e], v[s:e], tables, np.array([0, e - s]), w, sm_scale=scale)
             util.assert_close(o[s:e], ref, DT, f"tiny sequence {b}")
+
+
+def test_umma_repeated_runs_are_bitwise_identical():
+    """Work items are handed out dynamically, but every tile is computed in a fixed order: the output must not depend
+    on which CTA drew which item (a race on a staging row or a tensor-memory buffer would show up here)."""
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    w = _wl([512, 77, 300, 129, 64, 511, 1, 256], 512, hidden=256, heads=4, seed=55)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    lens = torch.as_tensor(np.asarray(w.lengths), dtype=torch.int32, device="cuda")
+    args = (q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), None, None, False, 0.0722, 256, 512)
+    first = flash_attention_with_disentangled(*args, seqlens=lens, tables=tables, kernel=UMMA).clone()
+    for _ in range(5):
+        again = flash_attention_with_disentangled(*args, seqlens=lens, tables=tables, kernel=UMMA)
+        assert torch.equal(first, again)
