@@ -82,3 +82,51 @@ def test_argument_errors():
         flash_attention_with_disentangled(q.cpu(), q.cpu(), q.cpu(), None, None)            # no CPU path
     with pytest.raises(NotImplementedError):
         flash_attention_with_disentangled(q, q, q, None, None, causal=True)
+
+
+def test_understated_max_seqlen_and_short_offsets_are_reported():
+    """The CUDA-core kernel sizes its grid from max_seqlen: a value below the longest sequence, or offsets that stop
+    short of the token count, must come back as an error instead of rows that were never written."""
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+    w = workloads.make_attention_workload("v", seed=22, hidden_size=128, num_heads=2, lengths=[40, 200],
+                                          padded_len=None, dtype=torch.float32)
+    q, k, v, rel, P = util.device_inputs(w, torch.float32)
+    tables = util.make_tables(w, rel, P)
+    cu = torch.as_tensor(w.cu_seqlens, device="cuda")
+    args = (False, 1.0 / (3 * 64) ** 0.5, 256, 512)
+    with pytest.raises(ValueError, match="max_seqlen"):
+        flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu, 64, 64, *args, tables=tables, kernel=SIMT)
+    short = cu.clone()
+    short[-1] -= 8
+    with pytest.raises(ValueError, match="cu_seqlens"):
+        flash_attention_with_disentangled_varlen(q, k, v, None, None, short, short, 200, 200, *args, tables=tables,
+                                                 kernel=SIMT)
+    other = cu.clone()
+    other[1] += 1                                          # key offsets that differ from the query offsets
+    with pytest.raises(ValueError, match="key offsets"):
+        flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, other, 200, 200, *args, tables=tables)
+    o = flash_attention_with_disentangled_varlen(q, k, v, None, None, cu, cu.clone(), 200, 200, *args, tables=tables)
+    assert torch.isfinite(o).all()
+
+
+def test_backward_raises_like_the_reference():
+    """Forward-only (the reference raises in backward, ``ops/flash_attention.py:341-343``): a loss built on the output
+    must fail loudly instead of training with no gradient through the attention."""
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+    q = torch.randn(1, 2, 16, 64, device="cuda", requires_grad=True)
+    o = flash_attention_with_disentangled(q, q.detach(), q.detach(), None, None)
+    assert o.requires_grad
+    with pytest.raises(RuntimeError, match="forward-only"):
+        o.sum().backward()
+    qp = torch.randn(16, 2, 64, device="cuda", requires_grad=True)
+    cu = torch.tensor([0, 16], dtype=torch.int32, device="cuda")
+    o = flash_attention_with_disentangled_varlen(qp, qp.detach(), qp.detach(), None, None, cu, cu, 16, 16)
+    with pytest.raises(RuntimeError, match="forward-only"):
+        o.sum().backward()
+    scores = torch.zeros(1, 2, 16, 512, device="cuda")
+    with pytest.raises(RuntimeError, match="forward-only"):           # score-tensor form: refused before the launch
+        flash_attention_with_disentangled(q, q, q, scores, None, position_buckets=256, max_relative_distance=512)
+    with torch.no_grad():
+        o = flash_attention_with_disentangled(q, q, q, scores, None, position_buckets=256, max_relative_distance=512)
+    assert not o.requires_grad

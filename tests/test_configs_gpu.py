@@ -99,3 +99,10 @@ def test_config5_packed_long_sequences():
     o_ref = _varlen(w, SIMT, q, k, v, tables)
     assert torch.isfinite(o.float()).all()
     assert (o.float() - o_ref.float()).abs().max().item() < 1e-2
+    # the oracle itself on one head of the shortest sequence (>= 2048 tokens: band tiles and saturated tiles)
+    s = int(np.argmin(w.lengths))
+    lo, hi = int(w.cu_seqlens[s]), int(w.cu_seqlens[s + 1])
+    ref = orc.attention_single(util.f64(q[lo:hi, :1]), util.f64(k[lo:hi, :1]), util.f64(v[lo:hi, :1]),
+                               util.f64(tables.kr[:1]), util.f64(tables.qr[:1]), position_buckets=256,
+                               max_relative_positions=512, sm_scale=1.0 / (3 * 64) ** 0.5)
+    util.assert_close(o[lo:hi, :1], ref, DT, f"config 5 packed, sequence {s} (length {hi - lo}), head 0")

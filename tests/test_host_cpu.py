@@ -114,3 +114,51 @@ def test_gather_two_ranks_gloo():
     port = _free_port()
     mp.spawn(_gather_worker, args=(world, port, ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_reference_import_paths_resolve_to_this_package():
+    """Code written against the reference imports ``turbodeberta.*`` (``src/turbodeberta/`` there): the alias package
+    serves the same module paths and names from this implementation."""
+    import turbodeberta.model as m
+    import turbodeberta.ops.flash_attention as fa
+    import turbodeberta.ops.flash_attention_varlen as fav
+    import turbodeberta.padding as pad
+    import turbodeberta_b200.model as ours
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    from turbodeberta_b200.ops.flash_attention_varlen import flash_attention_with_disentangled_varlen
+    assert m.FlashDebertaV2Model is ours.FlashDebertaV2Model
+    assert m.FlashDisentangledSelfAttention is ours.FlashDisentangledSelfAttention
+    for name in ("FlashDebertaV2Attention", "FlashDebertaV2Layer", "FlashDebertaV2Encoder", "FlashDebertaV2ForMaskedLM",
+                 "FlashDebertaV2ForSequenceClassification", "FlashDebertaV2ForTokenClassification",
+                 "FlashDebertaV2ForQuestionAnswering", "FlashDebertaV2ForMultipleChoice"):
+        assert getattr(m, name) is getattr(ours, name)
+    assert fa.flash_attention_with_disentangled is flash_attention_with_disentangled
+    assert fav.flash_attention_with_disentangled_varlen is flash_attention_with_disentangled_varlen
+    for name in ("pad_input", "unpad_input", "_upad_input", "index_first_axis", "index_put_first_axis", "_get_unpad_data"):
+        assert callable(getattr(pad, name))
+
+
+def test_pending_status_blocks_are_folded_never_dropped():
+    """Unchecked status blocks pile up only to a bound, and a report in the very first one survives the folding."""
+    from turbodeberta_b200.status import PendingStatus
+    q = PendingStatus()
+    first = torch.tensor([7, 0, 0, 0], dtype=torch.int32)
+    q.append(first)
+    for _ in range(3 * PendingStatus.FOLD_AT):
+        q.append(torch.zeros(4, dtype=torch.int32))
+    assert len(q) < PendingStatus.FOLD_AT
+    blocks = q.drain()
+    assert len(q) == 0
+    assert int(torch.stack(blocks).amax(dim=0)[0]) == 7
+
+
+def test_mask_analysis_refresh_recomputes_lengths_without_changing_the_route():
+    from turbodeberta_b200.model import analyse_mask
+    m = torch.zeros(2, 6, dtype=torch.long)
+    m[0, :6] = 1
+    m[1, :3] = 1
+    a = analyse_mask(m, 2, 6)
+    assert (a.all_ones, a.right_padded) == (False, True) and a.seqlens.tolist() == [6, 3]
+    b = analyse_mask(m, 2, 6, refresh=True)
+    assert b is not a and (b.all_ones, b.right_padded) == (False, True) and b.seqlens.tolist() == [6, 3]
+    assert analyse_mask(m, 2, 6) is b                      # the refreshed analysis is what later calls see

@@ -172,3 +172,84 @@ def test_encoder_forward_captures_into_a_cuda_graph():
     fresh = fwd()
     assert torch.equal(out, fresh)
     assert not torch.equal(out, eager)
+
+
+def _config4():
+    """Configuration 4's model: DeBERTa-v3-large geometry, random init."""
+    from transformers import DebertaV2Config
+    return DebertaV2Config(vocab_size=128100, hidden_size=1024, num_hidden_layers=24, num_attention_heads=16,
+                           intermediate_size=4096, hidden_act="gelu", relative_attention=True, position_buckets=256,
+                           max_relative_positions=-1, max_position_embeddings=512, norm_rel_ebd="layer_norm",
+                           share_att_key=True, pos_att_type=["p2c", "c2p"], position_biased_input=False, type_vocab_size=0)
+
+
+def test_config4_model_at_full_size_matches_eager():
+    """The 24-layer, hidden-1024, 16-head model of configuration 4 on 512-token sequences against the eager model in
+    fp32 on the host: bf16 on 2 x 512 tokens (tensor-core kernel), fp32 on 1 x 512 tokens (exact kernel)."""
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DebertaV2Model
+    from turbodeberta_b200.model import FlashDebertaV2Model
+    torch.manual_seed(1004)
+    cfg = _config4()
+    hf = DebertaV2Model(cfg).eval()
+    sd_bf = {k: v.to(torch.bfloat16) for k, v in hf.state_dict().items()}
+    hf.load_state_dict({k: v.float() for k, v in sd_bf.items()})          # fp32 model holding the bf16-rounded weights
+    gen = torch.Generator().manual_seed(1004)
+    ids = torch.randint(0, 128100, (2, 512), generator=gen)
+    mask = torch.ones_like(ids)
+    with torch.no_grad():
+        want = hf(input_ids=ids, attention_mask=mask).last_hidden_state
+    fl = FlashDebertaV2Model(cfg).eval()
+    fl.load_state_dict(hf.state_dict())
+    # fp32, one sequence
+    fl32 = fl.to("cuda")
+    with torch.no_grad():
+        got32 = fl32(input_ids=ids[:1].cuda(), attention_mask=mask[:1].cuda()).last_hidden_state.cpu()
+    rel = (got32 - want[:1]).abs().max().item() / want[:1].abs().max().item()
+    assert rel < util.MODEL_FP32_REL_TOL, rel
+    # bf16, both sequences; yardstick: the eager model in bf16 on the same GPU
+    flbf = fl32.to(torch.bfloat16)
+    with torch.no_grad():
+        got = flbf(input_ids=ids.cuda(), attention_mask=mask.cuda()).last_hidden_state.float().cpu()
+    del flbf, fl32, fl
+    eager_bf = DebertaV2Model(cfg).eval()
+    eager_bf.load_state_dict(hf.state_dict())
+    eager_bf = eager_bf.to("cuda", torch.bfloat16)
+    with torch.no_grad():
+        eag = eager_bf(input_ids=ids.cuda(), attention_mask=mask.cuda()).last_hidden_state.float().cpu()
+    del eager_bf
+    torch.cuda.empty_cache()
+    assert torch.isfinite(got).all()
+    err_ours, err_eager = (got - want).abs(), (eag - want).abs()
+    f = util.MODEL_BF16_VS_EAGER_FACTOR
+    assert err_ours.max().item() <= f * err_eager.max().item(), (err_ours.max().item(), err_eager.max().item())
+    assert err_ours.pow(2).mean().sqrt().item() <= f * err_eager.pow(2).mean().sqrt().item()
+
+
+def test_task_head_classes_run_on_the_gpu():
+    """The five head classes (broken constructors upstream, ``model.py:244-314``) through the fused kernels against
+    their eager counterparts with the same weights, fp32, padded batch."""
+    import transformers.models.deberta_v2.modeling_deberta_v2 as hfm
+    import turbodeberta_b200.model as ours
+    torch.manual_seed(11)
+    cfg = _cfg(num_labels=3)
+    ids = torch.randint(0, 500, (3, 96))
+    mask = torch.ones_like(ids)
+    mask[1, 50:] = 0
+    for name in ("ForMaskedLM", "ForSequenceClassification", "ForTokenClassification", "ForQuestionAnswering",
+                 "ForMultipleChoice"):
+        hf = getattr(hfm, "DebertaV2" + name)(cfg).eval()
+        fl = getattr(ours, "FlashDebertaV2" + name)(cfg).eval()
+        fl.load_state_dict(hf.state_dict())
+        x, m = (ids[None], mask[None]) if name == "ForMultipleChoice" else (ids, mask)       # [1, choices, L]
+        with torch.no_grad():
+            want = hf(input_ids=x, attention_mask=m)
+            got = fl.cuda()(input_ids=x.cuda(), attention_mask=m.cuda())
+        outs = [("start_logits", "end_logits")] if name == "ForQuestionAnswering" else [("logits",)]
+        for fields in outs:
+            for f in fields:
+                a, b = getattr(got, f).float().cpu(), getattr(want, f)
+                if name in ("ForMaskedLM", "ForTokenClassification", "ForQuestionAnswering"):       # per-token outputs
+                    v = mask.bool()
+                    a, b = a[v], b[v]
+                assert (a - b).abs().max().item() / max(b.abs().max().item(), 1e-6) < 5e-4, (name, f)
+        del hf, fl

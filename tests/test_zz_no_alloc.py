@@ -57,6 +57,29 @@ def _call(static, q, k, v, t, cu, max_len):
     return o
 
 
+def _assert_static_call_takes_no_device_memory(q, k, v, t, cu, max_len):
+    """The point of the entry point: a repeated call (the array's address is known by now) leaves the device's free
+    memory exactly as it found it.  The output and status tensors are made first, so that the only thing between the
+    two readings is the library call itself; the readings come from the driver, not from torch's caching allocator."""
+    from turbodeberta_b200 import _cabi as cabi
+    T, H, D = q.shape
+    o = torch.empty((T, H, D), dtype=DT, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    args = [cabi.ptr(q), cabi.ptr(k), cabi.ptr(v), cabi.ptr(o),
+            q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1), o.stride(0), o.stride(1),
+            cabi.ptr(t.kr), cabi.ptr(t.qr), t.two_span, cabi.ptr(t.idx), t.idx_delta_max,
+            cabi.ptr(t.kr_exp), cabi.ptr(t.qr_exp), t.exp_delta_max, t.exp_rows,
+            cabi.ptr(cu), cu.numel() - 1, T, max_len, H, D, 1.0 / (3 * 64) ** 0.5, 3, cabi.TDB_DTYPE_BF16, UMMA,
+            None, cabi.ptr(status), cabi.stream_ptr(q.device)]
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    cabi.check(cabi.lib.tdb_attn_fwd_varlen_static(*args))
+    free_during, _ = torch.cuda.mem_get_info()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_before == free_during == free_after, (free_before, free_during, free_after)
+
+
 def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
     # first call: many tiles; second call: fewer and different ones, so stale entries of the first call sit
     # behind the part of the list that the second call rewrites
@@ -65,6 +88,7 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
         mx = max(lengths)
         ref = _call(False, q, k, v, tables, cu, mx)
         got = _call(True, q, k, v, tables, cu, mx)
+        _assert_static_call_takes_no_device_memory(q, k, v, tables, cu, mx)
         assert torch.isfinite(got.float()).all()
         err = (got.float() - ref.float()).abs().max().item()
         assert err <= util.BF16_ABS_TOL, err

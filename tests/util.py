@@ -7,6 +7,14 @@ from turbodeberta_b200 import workloads
 
 BF16_ABS_TOL = 2e-2       # bf16 outputs vs the fp32/fp64 result on the same bf16-rounded inputs
 FP32_REL_TOL = 1e-4       # fp32 outputs: max |x - ref| / max |ref|
+# Whole models.  fp32: 24 layers of fp32 GEMMs on two different devices (different summation orders) on top of the
+# attention's 1e-4; measured differences sit near 1e-5, the bound leaves one order of magnitude.
+MODEL_FP32_REL_TOL = 5e-4
+# bf16: every layer rounds its activations to 8 bits of mantissa, so a 24-layer bf16 model is some 1e-2..1e-1 away
+# from the fp32 model whatever the attention kernel.  The yardstick is therefore the eager model ITSELF run in bf16:
+# the fused model may be at most this factor further from the fp32 result than eager-bf16 is (max abs and RMS), which
+# is what "the fused attention adds no error of its own" means at model level.
+MODEL_BF16_VS_EAGER_FACTOR = 1.5
 
 
 def f64(t: torch.Tensor) -> np.ndarray:

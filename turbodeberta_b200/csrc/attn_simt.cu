@@ -60,6 +60,11 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_kernel(const AttnPa
       if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicExch(p.status + 1, 1);
       return;
     }
+    // The grid covers max_seqlen rows per sequence: a longer sequence would leave rows unwritten, and offsets that
+    // do not end at the token count leave tokens outside every sequence.  Both are reported, not guessed around.
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 &&
+        (len > p.L || (s == p.n_seqs - 1 && (int64_t)c0 + len != p.total_tokens)))
+      atomicExch(p.status + 1, 1);
   } else {
     len = p.seqlens ? p.seqlens[s] : p.L; rows = p.L; tok0 = 0; b = s;
     len = len < 0 ? 0 : (len > p.L ? p.L : len);

@@ -17,6 +17,7 @@ one fused kernel call.  Differences from the reference module, all on the host s
 from __future__ import annotations
 
 import math
+import warnings
 import weakref
 
 import torch
@@ -64,20 +65,29 @@ def _mask_cache_put(tensor: torch.Tensor, info) -> None:
     _MASK_CACHE[id(tensor)] = (weakref.ref(tensor), tensor._version, info)
 
 
-def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int) -> MaskInfo:
+def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int, refresh: bool = False) -> MaskInfo:
     """Reduce a ``[B,L]``, ``[B,L,L]`` or ``[B,1,L,L]`` mask to per-row key validity.
 
-    Costs one device synchronisation (two booleans are read back); the result is cached on the mask
-    tensor object (weak reference) and its version, so the 24 layers of one forward share it.  A mask that is not the
-    outer product of a token-validity vector (i.e. whose valid queries disagree about the keys) is rejected."""
+    The first analysis of a mask costs one device synchronisation (two booleans are read back: all ones? right
+    padded?); the result is cached on the mask tensor object (weak reference) and its version, so the 24 layers of
+    one forward share it.  A mask that is not the outer product of a token-validity vector (i.e. whose valid queries
+    disagree about the keys) is rejected.
+
+    ``refresh=True`` (what the encoder passes once per forward) keeps the cached pair of booleans but recomputes the
+    length and validity tensors from the mask with synchronisation-free operations.  Inside a CUDA-graph capture that
+    puts the recomputation into the graph: replays then follow the lengths currently in the (static) mask buffer,
+    while the choice between the all-ones, right-padded and packed routes stays the one made at capture."""
     if attention_mask is None:
         return MaskInfo(True, True, None, None)
     key = id(attention_mask)
     hit = _MASK_CACHE.get(key)
+    flags = None
     if hit is not None:
         ref, version, cached = hit
         if ref() is attention_mask and version == attention_mask._version:     # same live tensor object, unmodified
-            return cached
+            if not refresh:
+                return cached
+            flags = (cached.all_ones, cached.right_padded)
     m = attention_mask
     if m.dim() == 4:
         if m.shape[1] != 1:
@@ -86,12 +96,13 @@ def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int) -
     if m.dim() == 3:
         full = m != 0
         key_mask = full.any(dim=1)                                  # a key is valid if any query may see it
-        query_mask = full.any(dim=2)
-        outer = key_mask[:, None, :] & query_mask[:, :, None]
-        consistent = torch.equal(outer, full) and torch.equal(key_mask, query_mask)
-        if not consistent:
-            raise ValueError("attention_mask is not of the form m (x) m^T for a token-validity vector m; "
-                             "the fused kernels support token padding masks only")
+        if flags is None:
+            query_mask = full.any(dim=2)
+            outer = key_mask[:, None, :] & query_mask[:, :, None]
+            consistent = torch.equal(outer, full) and torch.equal(key_mask, query_mask)
+            if not consistent:
+                raise ValueError("attention_mask is not of the form m (x) m^T for a token-validity vector m; "
+                                 "the fused kernels support token padding masks only")
     elif m.dim() == 2:
         key_mask = m != 0
     else:
@@ -99,11 +110,21 @@ def analyse_mask(attention_mask: torch.Tensor | None, batch: int, length: int) -
     if key_mask.shape != (batch, length):
         raise ValueError("attention_mask does not match the hidden states")
     seqlens = key_mask.sum(-1, dtype=torch.int32)
-    prefix = torch.arange(length, device=key_mask.device)[None, :] < seqlens[:, None]
-    flags = torch.stack([key_mask.all(), (prefix == key_mask).all()]).tolist()      # the one sync
+    if flags is None:
+        prefix = torch.arange(length, device=key_mask.device)[None, :] < seqlens[:, None]
+        flags = torch.stack([key_mask.all(), (prefix == key_mask).all()]).tolist()      # the one sync
     info = MaskInfo(bool(flags[0]), bool(flags[1]), seqlens, key_mask)
     _mask_cache_put(attention_mask, info)
     return info
+
+
+_WARNED: set = set()
+
+
+def _warn_once(key: str, message: str) -> None:
+    if key not in _WARNED:
+        _WARNED.add(key)
+        warnings.warn(message, stacklevel=3)
 
 
 class FlashDisentangledSelfAttention(DisentangledSelfAttention):
@@ -176,7 +197,14 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
         if query_states.shape[1] != L:
             raise NotImplementedError("query and key lengths must match (encoder self-attention)")
         H, D = self.num_attention_heads, self.attention_head_size
+        if self.training and float(getattr(self.dropout, "p", 0.0)) > 0.0:
+            _warn_once("dropout", "the fused attention has no dropout on the attention probabilities (neither has the "
+                       "reference's kernel) and no backward pass: attention_probs_dropout_prob is ignored")
         q, k, v = self._project_qkv(hidden_states, query_states)
+        if q.dtype == torch.float32 and B * L >= 4096:
+            _warn_once("fp32", "float32 inputs run on the exact CUDA-core attention kernel (one warp per query row), "
+                       "which is a correctness mode and far slower than the bf16 tensor-core kernel; "
+                       "convert the model with .bfloat16() for throughput")
         scale_factor = 1 + int("c2p" in self.pos_att_type) + int("p2c" in self.pos_att_type)
         sm_scale = 1.0 / math.sqrt(D * scale_factor)
         tables = None
@@ -248,7 +276,7 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
             # One analysis of the user's mask per forward (cached per mask tensor, so a repeated call with the same
             # tensor - e.g. while the forward is being captured into a CUDA graph - costs no synchronisation); the
             # expanded mask that the HF encoder builds from it inherits the result in get_attention_mask().
-            info = analyse_mask(attention_mask, hidden_states.shape[0], hidden_states.shape[1])
+            info = analyse_mask(attention_mask, hidden_states.shape[0], hidden_states.shape[1], refresh=True)
             if self.pack_padded_batches and not info.all_ones:
                 out = self._forward_packed(hidden_states, info, output_hidden_states, return_dict)
                 self._check_status_unless_capturing()

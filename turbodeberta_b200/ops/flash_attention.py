@@ -20,13 +20,13 @@ reproduces the reference kernel's mirrored position->content index (``ops/flash_
 """
 from __future__ import annotations
 
-import collections
 import math
 
 import torch
 
 from .. import _cabi as cabi
 from .. import relpos as _relpos
+from .. import status as _status
 
 
 def _tables_from_args(q_pos, k_pos, q, position_buckets, max_relative_distance, tables):
@@ -44,9 +44,8 @@ def _tables_from_args(q_pos, k_pos, q, position_buckets, max_relative_distance, 
             t = t[0]
         if t.dim() != 3 or t.shape[0] != H or t.shape[-1] != D:
             raise ValueError(
-                f"{name} must be the projected relative table of shape (H, 2*span, D) = ({H}, 2*span, {D}); got "
-                f"{tuple(t.shape)}. The materialised (B, H, L, 2*span) score tensors of the reference API are not "
-                "accepted: pass the tables and the products are formed inside the kernel.")
+                f"{name} must be the projected relative table of shape (H, 2*span, D) = ({H}, 2*span, {D}) or the "
+                f"materialised score tensor of q's leading shape with 2*span columns; got {tuple(t.shape)}.")
         return t.to(q.dtype).contiguous()
 
     kr, qr = norm(q_pos, "q_pos"), norm(k_pos, "k_pos")
@@ -101,10 +100,20 @@ def _index_table_for_scores(two_span, position_buckets, max_relative_distance, d
     return _relpos.bucket_index_table(position_buckets, max_relative_distance, sat + 1, dev), sat + 1
 
 
+def refuse_gradients(*tensors) -> None:
+    """The score-tensor form runs outside any autograd function, so nothing would stop a training loop from getting
+    an output without a gradient path; refuse it up front (the fused form raises in ``backward`` instead, like the
+    reference, ``ops/flash_attention.py:341-343``)."""
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise RuntimeError("turbodeberta_b200 attention is forward-only (as in the reference: no backward kernel); "
+                           "call it under torch.no_grad() or with detached inputs")
+
+
 def _scores_fixed(q, k, v, c2p_scores, p2c_scores, seqlens, sm_scale, position_buckets, max_relative_distance,
                   p2c_mirrored, return_lse, check_status):
     """Legacy form of the fixed-length op: gather from materialised ``(B, H, L, 2*span)`` score tensors."""
     dev = cabi.require_cuda(q, k, v, seqlens)
+    refuse_gradients(q, k, v, c2p_scores, p2c_scores)
     if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
         raise ValueError("q, k, v must share the shape (B, H, L, D)")
     B, H, L, D = q.shape
@@ -147,16 +156,14 @@ def _scores_fixed(q, k, v, c2p_scores, p2c_scores, seqlens, sm_scale, position_b
     return o, lse
 
 
-# Status words of calls made with check_status=False (no host sync at call time); read by check_pending_status().
-_PENDING_STATUS: collections.deque = collections.deque(maxlen=512)
+# Status words of calls made with check_status=False; read by check_pending_status().
+_PENDING_STATUS = _status.PENDING
 
 
 def check_pending_status() -> None:
     """Read (one synchronisation) the device status words of every call since the last check that was made
     with ``check_status=False`` and raise if any bounded device wait gave up or any ``cu_seqlens`` was malformed."""
-    pending = list(_PENDING_STATUS) + list(_relpos.PENDING_STATUS)
-    _PENDING_STATUS.clear()
-    _relpos.PENDING_STATUS.clear()
+    pending = _PENDING_STATUS.drain()
     if not pending:
         return
     by_dev = {}
@@ -172,7 +179,8 @@ def _check_status(status: torch.Tensor):
     if st[0]:
         raise cabi.TdbError(cabi.ERR_TIMEOUT, f"a device-side wait gave up (barrier code {st[0]})")
     if st[1]:
-        raise ValueError("cu_seqlens is not a non-decreasing sequence ending at the token count")
+        raise ValueError("cu_seqlens is not a non-decreasing sequence ending at the token count (or the key offsets "
+                         "differ from the query offsets, or max_seqlen is smaller than the longest sequence)")
 
 
 class _FixedFn(torch.autograd.Function):
@@ -222,8 +230,10 @@ class _FixedFn(torch.autograd.Function):
             _check_status(status)
         else:
             _PENDING_STATUS.append(status)
-        ctx.mark_non_differentiable(o)
-        return (o, lse, status) if return_lse else (o, None, status)
+        ctx.mark_non_differentiable(status)
+        if lse is not None:
+            ctx.mark_non_differentiable(lse)
+        return (o, lse, status)
 
     @staticmethod
     def backward(ctx, *grads):

@@ -21,12 +21,12 @@ import torch
 
 from .. import _cabi as cabi
 from .flash_attention import (_PENDING_STATUS, _check_status, _index_table_for_scores, _is_materialised,
-                              _tables_from_args)
+                              _tables_from_args, refuse_gradients)
 
 
 class _VarlenFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, tables, cu_seqlens, max_seqlen, sm_scale, kernel, return_lse, check):
+    def forward(ctx, q, k, v, tables, cu_seqlens, max_seqlen, sm_scale, kernel, return_lse, check, cu_seqlens_k=None):
         dev = cabi.require_cuda(q, k, v, cu_seqlens)
         if q.dim() != 3 or k.shape != q.shape or v.shape != q.shape:
             raise ValueError("q, k, v must share the shape (T, H, D)")
@@ -67,22 +67,35 @@ class _VarlenFn(torch.autograd.Function):
                 cabi.ptr(cu_seqlens), n_seqs, T, int(max_seqlen), H, D, float(sm_scale), flags, code, kernel,
                 cabi.ptr(ws), ws_bytes, cabi.ptr(lse), cabi.ptr(status), cabi.stream_ptr(dev))
         cabi.check(rc)
+        _flag_offset_mismatch(status, cu_seqlens, cu_seqlens_k)
         if check:
             _check_status(status)
         else:
             _PENDING_STATUS.append(status)
-        ctx.mark_non_differentiable(o)
-        return (o, lse, status) if return_lse else (o, None, status)
+        ctx.mark_non_differentiable(status)
+        if lse is not None:
+            ctx.mark_non_differentiable(lse)
+        return (o, lse, status)
 
     @staticmethod
     def backward(ctx, *grads):
         raise RuntimeError("turbodeberta_b200 attention is forward-only (as in the reference: no backward kernel)")
 
 
+def _flag_offset_mismatch(status, cu_q, cu_k) -> None:
+    """Self-attention only: key offsets must equal the query offsets.  When the caller passes two different tensors
+    the comparison runs on the device and lands in status word 1 (the malformed-offsets word), so the call itself
+    never waits for the GPU."""
+    if cu_k is None or cu_k is cu_q or (cu_k.data_ptr() == cu_q.data_ptr() and cu_k.shape == cu_q.shape):
+        return
+    status[1:2].add_((cu_k.to(cu_q.device) != cu_q).any().to(torch.int32))
+
+
 def _scores_varlen(q, k, v, c2p_scores, p2c_scores, cu_seqlens, max_seqlen, sm_scale, position_buckets,
-                   max_relative_distance, p2c_mirrored, return_lse, check_status):
+                   max_relative_distance, p2c_mirrored, return_lse, check_status, cu_seqlens_k=None):
     """Legacy form of the packed op: gather from materialised ``(T, H, 2*span)`` score tensors."""
     dev = cabi.require_cuda(q, k, v, cu_seqlens)
+    refuse_gradients(q, k, v, c2p_scores, p2c_scores)
     if q.dim() != 3 or k.shape != q.shape or v.shape != q.shape:
         raise ValueError("q, k, v must share the shape (T, H, D)")
     T, H, D = q.shape
@@ -118,6 +131,7 @@ def _scores_varlen(q, k, v, c2p_scores, p2c_scores, cu_seqlens, max_seqlen, sm_s
             cabi.ptr(cu_seqlens), n_seqs, T, max_seqlen, H, D, float(sm_scale), flags, code, cabi.ptr(lse),
             cabi.ptr(status), cabi.stream_ptr(dev))
     cabi.check(rc)
+    _flag_offset_mismatch(status, cu_seqlens, cu_seqlens_k)
     if check_status:
         _check_status(status)
     else:
@@ -133,7 +147,7 @@ def flash_attention_with_disentangled_varlen(q, k, v, q_pos, k_pos, cu_seqlens_q
     if causal:
         raise NotImplementedError("causal masking is not part of the DeBERTa encoder path")
     if cu_seqlens_k is not None and cu_seqlens_k is not cu_seqlens_q:
-        if cu_seqlens_k.shape != cu_seqlens_q.shape or not torch.equal(cu_seqlens_k, cu_seqlens_q):
+        if cu_seqlens_k.shape != cu_seqlens_q.shape or cu_seqlens_k.dtype != cu_seqlens_q.dtype:
             raise ValueError("query and key offsets must be equal: only self-attention is supported")
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
@@ -145,13 +159,13 @@ def flash_attention_with_disentangled_varlen(q, k, v, q_pos, k_pos, cu_seqlens_q
         if (q_pos is not None and not mat(q_pos)) or (k_pos is not None and not mat(k_pos)):
             raise ValueError("q_pos and k_pos must both be tables (H, 2*span, D) or both be score tensors (T, H, 2*span)")
         o, lse = _scores_varlen(q, k, v, q_pos, k_pos, cu_seqlens_q, max_seqlen, sm_scale, position_buckets,
-                                max_relative_distance, p2c_mirrored, return_lse, check_status)
+                                max_relative_distance, p2c_mirrored, return_lse, check_status, cu_seqlens_k)
         return (o, lse) if return_lse else o
     if p2c_mirrored:
         raise ValueError("p2c_mirrored applies to materialised score tensors only")
     tables = _tables_from_args(q_pos, k_pos, q, position_buckets, max_relative_distance, tables)
     o, lse, status = _VarlenFn.apply(q, k, v, tables, cu_seqlens_q, max_seqlen, sm_scale, kernel, return_lse,
-                                     check_status)
+                                     check_status, cu_seqlens_k)
     if return_lse:
         return o, lse
     return o

@@ -12,16 +12,15 @@ the result keyed on the weights' versions.
 """
 from __future__ import annotations
 
-import collections
 import math
 from dataclasses import dataclass
 
 import torch
 
 from . import _cabi as cabi
+from .status import PENDING as PENDING_STATUS
 
 _IDX_CACHE: dict = {}
-PENDING_STATUS: collections.deque = collections.deque(maxlen=512)
 
 
 def att_span(position_buckets: int, max_relative_positions: int) -> int:
