@@ -28,11 +28,10 @@ sys.path.insert(0, ROOT)
 
 METRIC = "disentangled_attn_algorithmic_tflops"
 UNIT = "TFLOP/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the attention kernel on the default workload,
-# from the ncu capture summarised in profiles/attn_umma_config2.md.
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu captures summarised in
-# profiles/attn_umma_config2.md (56.31 MB read + 4.9..5.1 MB written) and profiles/attn_umma_config3.md.
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the attention kernel, from an ncu capture of that
+# workload (c2: 56.31 MB read + 4.9..5.1 MB written; c3: one capture).  Workloads without a capture report null.
 NCU_TRAFFIC_BYTES = {"c2": 61.30e6, "c3": 525.5e6}
+NO_TRAFFIC_REASON = "no ncu capture of this workload (a launch holds more than the capture-size rule allows or was not captured)"
 
 
 def parse():
@@ -50,6 +49,10 @@ def parse():
     ap.add_argument("--no-packing", action="store_true", help="encoder workload: keep padded batches padded")
     ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "umma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-encoder", action="store_true", help="skip the configuration-4 encoder block of the default line")
+    ap.add_argument("--no-triton", action="store_true", help="skip timing the reference's Triton kernels (N=1 only)")
+    ap.add_argument("--no-tables", action="store_true", help="skip timing the once-per-layer table stage")
+    ap.add_argument("--encoder-steps", type=int, default=0, help="timed steps of the encoder block (0: at least 20, about 1.5 s)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="attention workloads: issue the op call from Python in every timed step instead of replaying it")
@@ -239,6 +242,86 @@ def cpu_baseline(w, budget_s=12.0):
         dt = time.perf_counter() - t0
         return {"value": sample.flops() / dt / 1e12, "unit": UNIT, "cores": 1, "kind": "port",
                 "sample": desc + f" (numpy port; eager module unavailable: {type(e).__name__})"}
+
+
+# ----------------------------------------------------------------------------------------------- side measurements
+def measure_tables(w, rel, P, dev, reps=20):
+    """The once-per-layer stage that replaces model.py:92-110 of the reference: bucket-index table, the two projections
+    of the relative embeddings and their two distance-expanded copies.  Replayed from a CUDA graph (so that the event
+    pair sees kernels, not the interpreter); bytes are the algorithmic ones of the five kernels."""
+    import torch
+    from turbodeberta_b200 import relpos
+
+    def build():
+        relpos._IDX_CACHE.clear()
+        return relpos.build_tables(rel, num_heads=w.num_heads, position_buckets=w.position_buckets,
+                                   max_relative_positions=w.max_relative_positions,
+                                   key_weight=P["key_proj.weight"], key_bias=P["key_proj.bias"],
+                                   query_weight=P["query_proj.weight"], query_bias=P["query_proj.bias"])
+    t = build()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        build()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        build()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    e, hid, ts, H, D = 2, w.hidden_size, w.two_span, w.num_heads, w.head_dim
+    proj = 2 * e * (hid * hid + ts * hid + ts * hid)                     # W, rel in; table out; two tables
+    expand = 2 * (e * ts * hid + 2 * H * t.exp_rows * D)                 # compact table in, expanded bf16 table out
+    bucket = 2 * (2 * t.idx_delta_max + 1)
+    flops = 2 * 2.0 * ts * hid * hid
+    return {"ms": ms, "kernels": 5, "algorithmic_bytes": proj + expand + bucket, "gbs": (proj + expand + bucket) / (ms * 1e-3) / 1e9,
+            "projection_gflop": flops / 1e9, "projection_bytes": proj, "expand_bytes": expand,
+            "what": "tdb_bucket_table + 2 x tdb_relpos_project + 2 x tdb_relpos_expand, replayed from a CUDA graph; "
+                    "runs once per layer and weight version, not per forward"}
+
+
+def triton_baseline(args):
+    """The reference's Triton kernels on this GPU (a separate process that imports the unmodified reference)."""
+    script = os.path.join(ROOT, "baseline", "triton_reference.py")
+    try:
+        r = subprocess.run([sys.executable, script, "--steps", "10", "--warmup", "3"], capture_output=True, text=True,
+                           timeout=420, cwd=ROOT)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "baseline/triton_reference.py did not finish within 420 s"}
+    for ln in reversed(r.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            try:
+                return json.loads(ln)
+            except ValueError:
+                break
+    return {"unavailable": f"no result (exit code {r.returncode}): {r.stderr.strip()[-300:]}"}
+
+
+def host_placement(local):
+    """Where this rank's host side lives: the CPUs it may run on, and the NUMA node its GPU hangs off (sysfs)."""
+    import torch
+    info = {"allowed_cpus": None, "gpu_numa_node": None}
+    try:
+        cpus = sorted(os.sched_getaffinity(0))
+        info["allowed_cpus"] = f"{cpus[0]}-{cpus[-1]} ({len(cpus)})" if cpus else None
+    except Exception:
+        pass
+    try:
+        pr = torch.cuda.get_device_properties(local)
+        with open(f"/sys/bus/pci/devices/{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0/numa_node") as f:
+            info["gpu_numa_node"] = int(f.read().strip())
+    except Exception:
+        pass
+    return info
 
 
 # ----------------------------------------------------------------------------------------------- our arm
@@ -500,15 +583,60 @@ def run_ours(args):
         barrier()
         e2e_ms = p0.elapsed_time(p1) / n_e2e
 
+        # What the copies cost on their own, with every rank copying at the same time (the ranks share the host's
+        # memory and its PCIe root ports): each direction alone, then both directions at once on two streams.
+        def copy_rate(up, down):
+            barrier()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for st in (s_in, s_out):
+                st.wait_stream(torch.cuda.current_stream())
+            c0.record(s_in)
+            s_out.wait_event(c0)
+            for _ in range(n_e2e):
+                if up:
+                    with torch.cuda.stream(s_in):
+                        xbuf[0].copy_(hidden_host, non_blocking=True)
+                if down:
+                    with torch.cuda.stream(s_out):
+                        hout.copy_(ybuf[0], non_blocking=True)
+            torch.cuda.current_stream().wait_stream(s_in)
+            torch.cuda.current_stream().wait_stream(s_out)
+            c1.record()
+            barrier()
+            return c0.elapsed_time(c1) / n_e2e
+        copy_ms = {"h2d_alone": copy_rate(True, False), "d2h_alone": copy_rate(False, True), "both": copy_rate(True, True)}
+
     flops = w.flops()
-    stats = torch.tensor([total_ms, flops, e2e_ms or 0.0], dtype=torch.float64, device=dev)
+    cm = copy_ms if e2e_ms is not None else {"h2d_alone": 0.0, "d2h_alone": 0.0, "both": 0.0}
+    stats = torch.tensor([total_ms, flops, e2e_ms or 0.0, cm["h2d_alone"], cm["d2h_alone"], cm["both"]],
+                         dtype=torch.float64, device=dev)
     if world > 1:
         mx_t = stats.clone(); dist.all_reduce(mx_t, op=dist.ReduceOp.MAX)
         sm_t = stats.clone(); dist.all_reduce(sm_t, op=dist.ReduceOp.SUM)
         total_ms, flops_all, e2e_max = float(mx_t[0]), float(sm_t[1]), float(mx_t[2])
+        cm = {"h2d_alone": float(mx_t[3]), "d2h_alone": float(mx_t[4]), "both": float(mx_t[5])}     # slowest rank
+        place = [None] * world
+        dist.all_gather_object(place, host_placement(local))
     else:
         flops_all, e2e_max = flops, e2e_ms or 0.0
-    status_ok = True
+        place = [host_placement(local)]
+
+    # ---- side measurements that ride in the same line: the once-per-layer table stage, the configuration-4 encoder
+    #      at this N (every rank takes part), and - on one GPU - the reference's Triton kernels ----
+    tables_blk = None
+    if rank == 0 and not args.no_tables:
+        try:
+            tables_blk = measure_tables(w, rel, P, dev)
+        except Exception as e:
+            tables_blk = {"unavailable": f"{type(e).__name__}: {e}"}
+    del flush
+    torch.cuda.empty_cache()
+    encoder_blk = None
+    if not args.no_encoder:
+        encoder_blk = measure_encoder(args, dev, world, rank, local, quick=True)
+    triton_blk = None
+    if rank == 0 and world == 1 and not args.no_triton:
+        triton_blk = triton_baseline(args)
 
     if rank == 0:
         pk = peaks()
@@ -536,10 +664,26 @@ def run_ours(args):
         if remeasured is not None:
             line["remeasured"] = remeasured
         if e2e_ms is not None:
+            gbs = lambda nbytes, ms: (nbytes / (ms * 1e-3) / 1e9) if ms > 0 else None
             line["e2e"] = {"value": flops_all / (e2e_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_max,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "call": e2e_api,
                            "pipeline": "upload / module call (replayed from a CUDA graph) / download of consecutive steps overlap on three streams",
-                           "unpipelined_ms_per_step": e2e_serial_ms}
+                           "unpipelined_ms_per_step": e2e_serial_ms,
+                           "h2d_gbs_per_rank_in_pipeline": gbs(h2d, e2e_max), "d2h_gbs_per_rank_in_pipeline": gbs(d2h, e2e_max),
+                           "copies_alone": {"what": "the step's copies without the module call, every rank copying at once; slowest rank",
+                                            "h2d_gbs_per_rank": gbs(h2d, cm["h2d_alone"]), "d2h_gbs_per_rank": gbs(d2h, cm["d2h_alone"]),
+                                            "both_directions_gbs_per_rank_each_way": gbs(h2d, cm["both"]),
+                                            "both_directions_ms_per_step": cm["both"]},
+                           "bound": ("host<->device copies" if cm["both"] > 0 and e2e_max < 1.25 * cm["both"] else "module call"),
+                           "host_placement_per_rank": place}
+        if tables_blk is not None:
+            line["tables"] = tables_blk
+        if encoder_blk is not None:
+            line["encoder"] = encoder_blk
+        if triton_blk is not None:
+            line["triton_baseline"] = triton_blk
+        if NCU_TRAFFIC_BYTES.get(args.workload) is None:
+            line["roofline"]["traffic_note"] = NO_TRAFFIC_REASON
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line), flush=True)
@@ -548,10 +692,13 @@ def run_ours(args):
 
 
 # ----------------------------------------------------------------------------------------------- encoder workload
-def run_encoder(args):
+def measure_encoder(args, dev, world, rank, local, quick=False):
     """DeBERTa-v3-large encoder forward with the patched attention (configuration 4): batch 256 x seq 512, bf16,
     random init, all-ones mask.  The batch is cut into contiguous slices, one per rank (strong scaling); every rank
-    runs its slice and the final hidden states are gathered over NCCL.  Metric: sequences per second."""
+    runs its slice and the final hidden states are gathered with one NCCL all_gather_into_tensor.  Returns, on every
+    rank, a dict with sequences per second (max over ranks of the event-timed step), the all-gather's own time
+    (events around the collective alone), the clock record of the timed region, and two checks of the gathered
+    output.  The process group must already exist when world > 1."""
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -560,13 +707,6 @@ def run_encoder(args):
     from turbodeberta_b200 import sharding
     from turbodeberta_b200.model import FlashDebertaV2Model
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     cfg = DebertaV2Config(vocab_size=128100, hidden_size=1024, num_hidden_layers=args.encoder_layers,
                           num_attention_heads=16, intermediate_size=4096, hidden_act="gelu", relative_attention=True,
                           position_buckets=256, max_relative_positions=-1, max_position_embeddings=512,
@@ -587,9 +727,9 @@ def run_encoder(args):
     model.encoder.pack_padded_batches = not args.no_packing
 
     @torch.no_grad()
-    def forward_local(model=model):
-        x = ids.to(dev, non_blocking=True)
-        return model(input_ids=x, attention_mask=mask).last_hidden_state
+    def forward_local(tok=ids, m=mask):
+        x = tok.to(dev, non_blocking=True)
+        return model(input_ids=x, attention_mask=m).last_hidden_state
 
     graph = None
     if args.encoder_graph:
@@ -605,16 +745,25 @@ def run_encoder(args):
         with torch.cuda.graph(graph):
             graph_out = forward_local()
 
+    gather_events = []
+
     @torch.no_grad()
-    def step():
+    def step(timed=False):
         if graph is not None:
             graph.replay()
             h = graph_out
         else:
             h = forward_local()
         if world > 1:
-            h = sharding.gather_padded(h, B)
-        return h
+            if timed:
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                g0.record()
+            full = sharding.gather_padded(h, B)
+            if timed:
+                g1.record()
+                gather_events.append((g0, g1))
+            return h, full
+        return h, h
 
     def barrier():
         if world > 1:
@@ -624,25 +773,53 @@ def run_encoder(args):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:                                   # before the warm-up: no idle gap between warm-up and timed region
         sampler.start(); time.sleep(1.5)
-    for _ in range(max(3, args.warmup)):
-        out = step()
+    n_warm = max(3, args.warmup if not quick else 3)
+    t_w0 = time.time()
+    for _ in range(n_warm):
+        local_out, out = step()
     barrier()
+    est_ms = (time.time() - t_w0) / n_warm * 1e3
     assert torch.isfinite(out.float()).all()
+    steps = args.encoder_steps if args.encoder_steps > 0 else (args.steps if not quick else 0)
+    if steps <= 0:                                # at least 20 steps and about 1.5 s, so that the clock sampler sees the region
+        steps = int(min(200, max(20, 1500.0 / max(est_ms, 1e-3))))
+    nst = torch.tensor([steps], device=dev)
+    if world > 1:
+        dist.broadcast(nst, 0)
+    steps = int(nst.item())
+    barrier()
     w0 = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        out = step()
+    for _ in range(steps):
+        local_out, out = step(timed=True)
     e1.record()
     barrier()
     w1 = time.time()
-    ms = e0.elapsed_time(e1) / args.steps
-    checksum = float(out.float().abs().mean())          # device -> host read of the result
+    ms = e0.elapsed_time(e1) / steps
+    gather_ms = (sum(a.elapsed_time(b) for a, b in gather_events) / steps) if gather_events else 0.0
     clocks = sampler.stop(w0, w1) if sampler else None
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    # Checks of the gathered output (device -> host reads of the result).  (1) this rank's slice of the gathered tensor
+    # is bit for bit its own output; (2) rank 0 runs the LAST rank's slice itself, with the same per-GPU batch shape,
+    # and compares it bit for bit with what arrived through the gather.  Position-weighted checksums in float64 are
+    # reported so that runs at different N can be compared (they agree to rounding: GEMM tile choices depend on the
+    # per-GPU batch).
+    own_ok = bool(torch.equal(out[sl], local_out))
+    cross = None
+    if world > 1:
+        last = sharding.shard_batch(B, world, world - 1)
+        if rank == 0:
+            with torch.no_grad():
+                theirs = forward_local(ids_all[last].pin_memory(), mask)
+            cross = float((theirs.float() - out[last].float()).abs().max())
+    o64 = out.double()
+    wts = torch.arange(1, o64.shape[0] + 1, device=dev, dtype=torch.float64)[:, None, None]
+    checksum = {"abs_mean": float(o64.abs().mean()), "weighted_sum": float((o64 * wts).sum()),
+                "first_row_sum": float(o64[0].sum()), "last_row_sum": float(o64[-1].sum())}
+    t = torch.tensor([ms, gather_ms, 0.0 if own_ok else 1.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0])
+    ms, gather_ms, any_bad = float(t[0]), float(t[1]), float(t[2])
     eager = None
     if args.with_eager and rank == 0:
         hf = DebertaV2Model(cfg).eval().to(dev, torch.bfloat16)
@@ -659,18 +836,44 @@ def run_encoder(args):
             eager = {"seq_per_s": n / ((time.perf_counter() - t0) / 3), "batch": n,
                      "what": "unpatched transformers DebertaV2Model (eager attention), bf16, same GPU"}
         del hf
+    res = {"workload": f"c4_v3large_{args.encoder_layers}layers_b{B}_l512_" +
+                       ("ragged64to512" + ("_padded" if args.no_packing else "_packed") if args.encoder_ragged else "allones"),
+           "global_batch": B, "seq_len": L, "n_gpus": world, "scaling": "strong",
+           "parallelism": f"batch shards x{world}, one NCCL all_gather_into_tensor of the final hidden states",
+           "seq_per_s": B / (ms * 1e-3), "ms_per_step": ms, "steps": steps, "warmup": n_warm,
+           "allgather_ms": gather_ms, "allgather_share": gather_ms / ms if ms > 0 else None,
+           "allgather_bytes_per_rank": int(local_out.numel() * local_out.element_size()),
+           "h2d_bytes_per_step": int(ids.numel() * 8), "cuda_graph": bool(args.encoder_graph),
+           "gathered_slice_equals_local_output_on_every_rank": any_bad == 0.0,
+           "last_shard_recomputed_on_rank0_max_abs_diff": cross,
+           "checksum": checksum, "clocks": clocks, "eager_gpu": eager}
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_encoder(args):
+    """`--workload encoder`: the encoder measurement as a line of its own."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    r = measure_encoder(args, dev, world, rank, local)
     if rank == 0:
-        line = {"metric": "deberta_v3_large_encoder_seq_per_s", "value": B / (ms * 1e-3), "unit": "seq/s", "n_gpus": world,
-                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+        line = {"metric": "deberta_v3_large_encoder_seq_per_s", "value": r["seq_per_s"], "unit": "seq/s", "n_gpus": world,
+                "steps": r["steps"], "warmup": r["warmup"], "ms_per_step": r["ms_per_step"], "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"c4_v3large_{args.encoder_layers}layers_b{B}_l512_" +
-                           ("ragged64to512" + ("_padded" if args.no_packing else "_packed") if args.encoder_ragged else "allones"),
-                           "global_batch": B,
-                           "seq_len": L, "parallelism": f"batch shards x{world}, NCCL all-gather of outputs", "cuda_graph": bool(args.encoder_graph),
+                "config": {"workload": r["workload"], "global_batch": r["global_batch"], "seq_len": r["seq_len"],
+                           "parallelism": r["parallelism"], "cuda_graph": r["cuda_graph"],
                            "l2": "activations of one step (hundreds of MB) exceed L2"},
-                "e2e": {"value": B / (ms * 1e-3), "unit": "seq/s", "h2d_bytes_per_step": int(ids.numel() * 8),
-                        "d2h_bytes_per_step": 4, "note": "token ids copied from pinned host memory every step"},
-                "output_abs_mean": checksum, "clocks": clocks, "eager_gpu": eager}
+                "e2e": {"value": r["seq_per_s"], "unit": "seq/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                        "d2h_bytes_per_step": 32, "note": "token ids copied from pinned host memory every step"},
+                "encoder": r, "clocks": r["clocks"], "eager_gpu": r["eager_gpu"]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -48,6 +48,8 @@ def gather_padded(local: torch.Tensor, n_total: int, group=None) -> torch.Tensor
         buf[: local.shape[0]] = local
     out = torch.empty(world * biggest, *local.shape[1:], dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(out, buf.contiguous(), group=group)
+    if world * biggest == n_total:                 # even slices: the collective's output already is the result
+        return out
     parts = [out[r * biggest: r * biggest + (s.stop - s.start)] for r, s in enumerate(sizes)]
     return torch.cat(parts, 0)
 
