@@ -12,35 +12,26 @@
 // KrX / QrX are the distance-expanded tables (row x <-> distance x - exp_delta_max), so the rows a tile
 // needs are the contiguous window win = [q0 - k0 - 127 + exp_delta_max, +256), one TMA box.  The diagonal
 // read C[i][i-j+127] cannot be done from registers (the column depends on the lane), so both bands are
-// drained from tensor memory to shared memory as bf16 rows.  Tiles whose distances are all
+// drained from tensor memory to shared memory as bf16 rows and read back skewed.  Tiles whose distances are all
 // saturated need one value per query row / per key instead of a band (long-sequence variant of the kernel).
 //
-// Warp roles (864 threads): warps 0-15 = softmax (warp w owns tensor-memory lanes 32*(w%4)..+31 = query rows, and
-// key group w/4: four threads share a query row and each handles 32 of the 128 keys); warps 16-23 = band drains (two
-// per lane quadrant, 80 band columns each); warp 24 = tensor-memory allocation + issue of the two band products of
-// every key tile (one lane); warp 26 = issue of the score and P.V products (one lane; the band lane spends its time
-// waiting for the drains, and the scores must not queue behind that); warp 25 = scheduler (draws work items from a
-// device-wide counter, publishes them in a shared-memory ring, zeroes tiles that consist of padded rows only; hands
-// the padded form's sequences out longest first).  There is no producer role: each bulk load is issued by the MMA
-// lane that consumes the operand, at the moment that lane learns that the buffer is free (a single thread on a busy
-// scheduler takes a microsecond to notice a released buffer and react, and that sat on every tile's critical path).
-//
-// The diagonal reads C[i][i-j+127] / P2[j][i-j+127] need a per-row shift that neither tensor memory nor registers can
-// index, so each band goes through shared memory once: a drain warp copies its 32 rows of the band (the 160 columns
-// those rows can need) to staging rows as bf16, and the softmax warps read them back skewed - 32-bit words realigned
-// with one funnel shift for the c2p term (own row, descending keys), one 16-bit cell per key for the p2c term (a
-// column of the key rows).  Drains and softmax run concurrently on different key tiles, coupled only by per-quadrant
-// full/free mbarriers.
+// Warp roles (608 threads): warps 0-15 do the CUDA-core work; warp w owns tensor-memory lanes 32*(w%4)..+31
+// (query rows, or key rows of P2) and column group w/4, i.e. four threads share a query row and each handles 32
+// of the 128 keys, which puts four warps on every scheduler to hide latency.  Warp 16 = TMA producers (lane 0:
+// tables and K, lane 1: V, lane 2: Q), warp 17 = tensor-memory allocation + MMA issue (one lane), warp 18 =
+// scheduler (draws work items from a device-wide counter, publishes them in a shared-memory ring, zeroes tiles
+// that consist of padded rows only).
 //
 // Pipeline: the MMA lane issues C(0) S(0) P2(0) C(1) | S(g+1) P2(g+1) C(g+2) PV(g) | ..., so the bands and scores
-// of the next key tiles are produced while the softmax warps work on tile g; C and P2 of a tile pass through the one
-// band buffer in tensor memory (one full/free barrier pair).  The softmax warps walk one flat stream of key tiles
-// across work items: per tile they add the c2p term, add the p2c term and take the exponentials against the
-// reference exponent of the tiles before (a voting barrier tells whether any row has to move it) and store P.  The
-// epilogue of an item (O / l, staged in shared memory so that whole 128-byte rows are stored) runs inside the first
-// tile of the next item, where the wait for its last P.V product costs nothing.
+// of the next key tiles are produced while the CUDA warps work on tile g; C and P2 of a tile pass through the one
+// band buffer in tensor memory (one full/free barrier pair), each drained to its staging rows - 40 columns per
+// warp - before the other is issued.  The CUDA warps walk one flat stream of key tiles across work items: per
+// tile they add the c2p term, drain C of the next tile, add the p2c term and take the exponentials against the
+// reference exponent of the tiles before (a voting barrier tells whether any row has to move it), store P and
+// drain P2 of the next tile.  The epilogue of an item (O / l, staged in shared memory so that whole 128-byte rows
+// are stored) runs inside the first tile of the next item, where the wait for its last P.V product costs nothing.
 // All hand-offs are mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort flag and the status
-// word, after which every role runs out its loops without waiting (the softmax warps take their trip counts from
+// word, after which every role runs out its loops without waiting (the CUDA warps take their trip counts from
 // one copy of the work items kept by thread 0, so their named barriers still match), tensor memory is freed, and
 // the host reports TDB_ERR_TIMEOUT.
 //
@@ -57,46 +48,41 @@ using namespace ptx;
 namespace {
 
 constexpr int BQ = 128, BK = 128, HD = 64, BAND = 256;
-constexpr int GROUPS = 4;                       // threads per query row
+#ifndef TDB_GROUPS
+#define TDB_GROUPS 4
+#endif
+constexpr int GROUPS = TDB_GROUPS;              // threads per query row (2 or 4)
+static_assert(GROUPS == 4, "four threads per query row (the drain split and the staging windows assume it)");
 constexpr int KPT = BK / GROUPS;                // keys per thread in the softmax
 constexpr int OPT = HD / GROUPS;                // output columns per thread
-constexpr int NSW = 4 * GROUPS;                 // softmax warps
-constexpr int NDW = 8;                          // band-drain warps: two per tensor-memory lane quadrant, 80 band columns each
-constexpr int NST = NSW * 32;                   // softmax threads
-constexpr int W_DRAIN = NSW, W_BAND = NSW + NDW, W_SCHED = W_BAND + 1, W_SPV = W_BAND + 2;
-constexpr int NTHREADS = (NSW + NDW + 3) * 32;
+constexpr int NCW = 4 * GROUPS;                 // CUDA-core warps
+constexpr int NCT = NCW * 32;                   // CUDA-core threads
+constexpr int NTHREADS = (NCW + 3) * 32;       // + TMA producer warp, MMA warp, scheduler warp
 constexpr int STG_STRIDE = 336;                 // bytes per staging row: 160 bf16 + 16 pad (odd multiple of 16)
 constexpr int STG_COLS = 160;
 constexpr uint32_t OFF_Q = 0 /* two buffers */, OFF_K = 32768, OFF_V = 49152, OFF_KR = 65536, OFF_QR = 98304;
-constexpr uint32_t TILE_BYTES = BQ * HD * 2;
 constexpr uint32_t OFF_STC = 131072, OFF_STP = OFF_STC + BQ * STG_STRIDE, OFF_XCH = OFF_STP + BK * STG_STRIDE;
-constexpr uint32_t OFF_SAT = OFF_XCH + GROUPS * BQ * 4;     // saturated tiles: one c2p value per query row, one p2c value per key
-constexpr uint32_t OFF_BAR = OFF_SAT + 2 * BQ * 4;
-constexpr uint32_t OFF_WORK = OFF_BAR + 512;        // ring of work items published by the scheduler lane
-constexpr uint32_t OFF_CUR = OFF_WORK + 256;        // abort flag, tensor-memory base, the softmax warps' copies of their items
+constexpr uint32_t OFF_BAR = OFF_XCH + GROUPS * BQ * 4;
+constexpr uint32_t OFF_WORK = OFF_BAR + 256;        // ring of work items published by the scheduler lane
+constexpr uint32_t OFF_CUR = OFF_WORK + 256;        // abort flag, tensor-memory base, the CUDA-core warps' copies of their items
 constexpr uint32_t OFF_LX = OFF_CUR + 160;          // row-sum partials of a finished item, [item parity][group][row]
 constexpr uint32_t OFF_MX = OFF_LX + 2 * GROUPS * BQ * 4;   // its reference exponents, [item parity][row]
 constexpr uint32_t OFF_PERM = OFF_MX + 2 * BQ * 4;          // padded form: sequences by decreasing length
 constexpr int PERM_MAX = 256;
 constexpr uint32_t SMEM_BYTES = OFF_PERM + PERM_MAX * 2 + 1024;   // + slack for the 1024-byte alignment of the base
-static_assert(OFF_STP % 16 == 0 && OFF_XCH % 16 == 0 && OFF_BAR % 16 == 0 && OFF_CUR % 16 == 0 && OFF_LX % 16 == 0,
-              "offsets must stay 16-byte aligned");
+static_assert(OFF_STP % 16 == 0 && OFF_XCH % 16 == 0 && OFF_BAR % 16 == 0 && OFF_LX % 16 == 0, "offsets must stay 16-byte aligned");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 constexpr uint32_t TM_S = 0, TM_O = 128, TM_RING = 192, TM_P = 448, TM_COLS = 512;
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per wait, then give up
 
-enum Bar { Q_FULL = 0 /* + buffer */, Q_FULL1, Q_EMPTY /* + buffer */, Q_EMPTY1, K_FULL, K_EMPTY /* the score product has read K */,
-           V_FULL, V_EMPTY, KR_FULL, QR_FULL,
+enum Bar { Q_FULL = 0 /* Q_FULL + buffer */, Q_FULL1, Q_EMPTY /* Q_EMPTY + buffer */, Q_EMPTY1, K_FULL, K_EMPTY, V_FULL, V_EMPTY, KR_FULL, KR_EMPTY, QR_FULL, QR_EMPTY,
            S_FULL, S_TAKEN, BAND_FULL, BAND_FREE, P_READY, O_FULL,
-           DONE, DONE_PV, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
-           WORK_EMPTY0, WORK_EMPTY1, WORK_EMPTY2, WORK_EMPTY3,
-           STC_FULL0 /* + quadrant of query rows */, STC_FULL1, STC_FULL2, STC_FULL3, STC_FREE0, STC_FREE1, STC_FREE2, STC_FREE3,
-           STP_FULL0 /* + quadrant of key rows */, STP_FULL1, STP_FULL2, STP_FULL3, STP_FREE0, STP_FREE1, STP_FREE2, STP_FREE3,
-           NBARS };
+           DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
+           WORK_EMPTY0, WORK_EMPTY1, WORK_EMPTY2, WORK_EMPTY3, NBARS };
 constexpr int WORK_RING = 4;
-constexpr int WORK_READERS = 2 + 1 + NDW;       // the two MMA lanes, the softmax warps' leader, the drain warps
-static_assert(NBARS * 8 <= 512, "barrier block");
+constexpr int WORK_READERS = 3 + 1 + 1;         // three producer lanes, the MMA lane, the CUDA-core warps' leader
+static_assert(NBARS * 8 <= 256, "barrier block");
 
 struct TileListHeader { int32_t n_tiles; int32_t pad[3]; };
 
@@ -146,13 +132,6 @@ __device__ __forceinline__ float add_bf16(float x, uint16_t h) {
   asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(y) : "h"(h), "f"(x));
   return y;
 }
-// x + both halves of a packed bf16 pair.
-__device__ __forceinline__ void add_bf16x2(float& x_lo, float& x_hi, uint32_t packed) {
-  uint16_t lo, hi;
-  asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(packed));
-  x_lo = add_bf16(x_lo, lo);
-  x_hi = add_bf16(x_hi, hi);
-}
 __device__ __forceinline__ uint16_t lds_u16(uint32_t addr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
@@ -179,11 +158,9 @@ __device__ __forceinline__ uint4 lds_128(uint32_t addr) {
 __device__ __forceinline__ void sts_128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-// Makes this thread's earlier shared-memory writes visible to the asynchronous proxy (the tensor cores' operand fetch).
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void bar_softmax_warps() { asm volatile("bar.sync 1, %0;" ::"n"(NST) : "memory"); }
+__device__ __forceinline__ void bar_all_cuda_warps() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 // The same barrier with an OR-reduction of one predicate per thread.
-__device__ __forceinline__ bool bar_softmax_warps_or(bool flag) {
+__device__ __forceinline__ bool bar_all_cuda_warps_or(bool flag) {
   uint32_t r;
   asm volatile(
       "{\n"
@@ -192,9 +169,10 @@ __device__ __forceinline__ bool bar_softmax_warps_or(bool flag) {
       "bar.red.or.pred p, 1, %2, q;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}"
-      : "=r"(r) : "r"((uint32_t)flag), "n"(NST) : "memory");
+      : "=r"(r) : "r"((uint32_t)flag), "n"(NCT) : "memory");
   return r != 0;
 }
+__device__ __forceinline__ void bar_quadrant(int qd) { asm volatile("bar.sync %0, %1;" ::"r"(2 + qd), "n"(GROUPS * 32) : "memory"); }
 
 // N consecutive 32-bit columns of this thread's tensor-memory lane (N = 16, 32 or 64).
 template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
@@ -214,32 +192,20 @@ template <int N> __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, co
   }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Band drain: NCOLS consecutive fp32 columns of this thread's tensor-memory lane -> NCOLS bf16 of a staging row, in
-// chunks of 16 columns, the next chunk's load in flight while the current one is packed and stored.
-template <int NCOLS>
-__device__ __forceinline__ void drain_band_row(uint32_t taddr, uint32_t dst_saddr) {
-  static_assert(NCOLS % 16 == 0, "whole chunks");
-  uint32_t va[16], vb[16];
-  tmem_ld16(taddr, va);
+// Move 32 fp32 columns of this thread's tensor-memory lane to 32 bf16 of a staging row.
+__device__ __forceinline__ void drain_chunk(uint32_t taddr, uint32_t dst_saddr) {
+  uint32_t r[32];
+  tmem_ld32(taddr, r);
+  tmem_ld_wait32(r);
 #pragma unroll
-  for (int c = 0; c < NCOLS / 16; ++c) {
-    uint32_t* cur = (c & 1) ? vb : va;
-    uint32_t* nxt = (c & 1) ? va : vb;
-    tmem_ld_wait16(cur);
-    if (c + 1 < NCOLS / 16) tmem_ld16(taddr + 16u * (uint32_t)(c + 1), nxt);
+  for (int g = 0; g < 4; ++g) {
+    uint32_t w[4];
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        w[e] = pack_bf16x2(__uint_as_float(cur[g * 8 + 2 * e]), __uint_as_float(cur[g * 8 + 2 * e + 1]));
-      sts_128(dst_saddr + 32u * (uint32_t)c + 16u * (uint32_t)g, w[0], w[1], w[2], w[3]);
-    }
+    for (int e = 0; e < 4; ++e)
+      w[e] = pack_bf16x2(__uint_as_float(r[g * 8 + 2 * e]), __uint_as_float(r[g * 8 + 2 * e + 1]));
+    sts_128(dst_saddr + g * 16, w[0], w[1], w[2], w[3]);
   }
 }
-constexpr int DRAIN_COLS = STG_COLS / (NDW / 4);     // band columns per drain warp
-static_assert(NDW % 4 == 0 && DRAIN_COLS % 16 == 0, "drain split");
 
 // One unit of work: a 128-query tile of one sequence for one head.
 // A 128x128 score tile whose distances q - k all lie at or beyond the saturation distance (on one side): every
@@ -297,14 +263,13 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
                                    : p.n_seqs * ((p.L + BQ - 1) / BQ);
   // An earlier CTA gave up: the scheduler lane (which reads the word while the CTA sets itself up) hands out no work.
   int32_t status_at_start = 0;
-  if (warp == W_SCHED && lane == 0) status_at_start = *reinterpret_cast<volatile int32_t*>(p.status);
+  if (warp == NCW + 2 && lane == 0) status_at_start = *reinterpret_cast<volatile int32_t*>(p.status);
 
   // ---- shared memory carve-up ----------------------------------------------------------------
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t sQ = sbase + OFF_Q, sK = sbase + OFF_K, sV = sbase + OFF_V, sKr = sbase + OFF_KR, sQr = sbase + OFF_QR;
   const uint32_t stC = sbase + OFF_STC, stP = sbase + OFF_STP, sX = sbase + OFF_XCH;
-  const uint32_t satC = sbase + OFF_SAT, satP = satC + BQ * 4;
   const uint32_t bars = sbase + OFF_BAR;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OFF_CUR);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + OFF_CUR + 8);
@@ -315,23 +280,18 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < NBARS; ++i) {
-      uint32_t count = 1;
-      if (i == S_TAKEN || i == P_READY) count = NSW;
-      else if (i == BAND_FREE) count = NDW;
-      else if (i >= WORK_EMPTY0 && i <= WORK_EMPTY3) count = WORK_READERS;
-      else if (i == Q_EMPTY || i == Q_EMPTY1) count = C2P ? 2 : 1;   // the score lane and the band lane both read Q
-      else if ((i >= STC_FREE0 && i <= STC_FREE3) || (i >= STP_FREE0 && i <= STP_FREE3)) count = GROUPS;
-      else if ((i >= STC_FULL0 && i <= STC_FULL3) || (i >= STP_FULL0 && i <= STP_FULL3)) count = NDW / 4;
-      mbar_init(bar(i), count);
+      const bool by_warps = (i == S_TAKEN || i == BAND_FREE || i == P_READY);
+      const bool by_readers = (i >= WORK_EMPTY0 && i <= WORK_EMPTY3);
+      mbar_init(bar(i), by_readers ? (uint32_t)WORK_READERS : (by_warps ? (uint32_t)NCW : 1u));
     }
     fence_mbar_init();
   }
-  if (warp == W_SPV && lane == 0) {
+  if (warp == NCW && lane == 0) {
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
     if (C2P) { prefetch_tmap(&tm_kr); prefetch_tmap(&tm_kr16); }
     if (P2C) { prefetch_tmap(&tm_qr); prefetch_tmap(&tm_qr16); }
   }
-  if (warp == W_BAND) {
+  if (warp == NCW + 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TM_COLS);
     tmem_relinquish();
   }
@@ -349,14 +309,80 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     return k.n_kv > 0;
   };
   auto release = [&](int n) { mbar_arrive(bar(WORK_EMPTY0 + (n % WORK_RING))); };
+  auto next_tensor_item = [&](int& n, Work& k) { return fetch(n, k); };
 
-  if (warp == W_SCHED) {
+  if (warp == NCW) {
+    // ================================ TMA producers ==========================================
+    if (lane == 0) {                       // relative tables and K, once per key tile
+      Work k;
+      int g = 0, n = 0;
+      while (next_tensor_item(n, k)) {
+        for (int it = 0; it < k.n_kv; ++it, ++g) {
+          const int k0 = it * BK;
+          const uint32_t pe = (uint32_t)((g - 1) & 1);
+          int x0 = k.q0 - k0 - (BK - 1) + p.exp_delta_max;
+          x0 = x0 < 0 ? 0 : (x0 > p.exp_rows - BAND ? p.exp_rows - BAND : x0);
+          const bool sat = LONG && tile_saturated(p, k.q0, k0);
+          if (C2P) {
+            if (g > 0) wait(KR_EMPTY, pe);
+            if (!*abort_flag) {
+              mbar_expect_tx(bar(KR_FULL), (sat ? SATN : BAND) * HD * 2);
+              tma_load_3d(sKr, sat ? &tm_kr16 : &tm_kr, bar(KR_FULL), 0, x0, k.h);
+            }
+          }
+          if (g > 0) wait(K_EMPTY, pe);
+          if (!*abort_flag) {
+            mbar_expect_tx(bar(K_FULL), BK * HD * 2);
+            tma_load_4d(sK, &tm_k, bar(K_FULL), 0, (int)(k.tok0 + k0), k.h, k.bcoord);
+          }
+          if (P2C) {
+            if (g > 0) wait(QR_EMPTY, pe);
+            if (!*abort_flag) {
+              mbar_expect_tx(bar(QR_FULL), (sat ? SATN : BAND) * HD * 2);
+              tma_load_3d(sQr, sat ? &tm_qr16 : &tm_qr, bar(QR_FULL), 0, x0, k.h);
+            }
+          }
+        }
+        release(n);
+        ++n;
+      }
+      release(n);
+    } else if (lane == 1) {                // V, once per key tile
+      Work k;
+      int g = 0, n = 0;
+      while (next_tensor_item(n, k)) {
+        for (int it = 0; it < k.n_kv; ++it, ++g) {
+          if (g > 0) wait(V_EMPTY, (uint32_t)((g - 1) & 1));
+          if (!*abort_flag) {
+            mbar_expect_tx(bar(V_FULL), BK * HD * 2);
+            tma_load_4d(sV, &tm_v, bar(V_FULL), 0, (int)(k.tok0 + it * BK), k.h, k.bcoord);
+          }
+        }
+        release(n);
+        ++n;
+      }
+      release(n);
+    } else if (lane == 2) {                // Q, once per work item, into alternating buffers
+      Work k;
+      int n = 0;
+      while (next_tensor_item(n, k)) {
+        const int b = n & 1;
+        if (n >= 2) wait(Q_EMPTY + b, (uint32_t)(((n >> 1) - 1) & 1));
+        if (!*abort_flag) {
+          mbar_expect_tx(bar(Q_FULL + b), BQ * HD * 2);
+          tma_load_4d(sQ + (uint32_t)b * (BQ * HD * 2), &tm_q, bar(Q_FULL + b), 0, (int)(k.tok0 + k.q0), k.h, k.bcoord);
+        }
+        release(n);
+        ++n;
+      }
+      release(n);
+    }
+  } else if (warp == NCW + 2) {
     // ================================ scheduler ==============================================
     // Draws work items from the device-wide counter and publishes those with tensor work in the ring; tiles made of
     // padded query rows only (padded form) are zeroed here by the whole warp and never reach the other roles.
     // The first item of a CTA is its own index (no round trip to the counter before the pipeline can start); the
     // counter hands out the items after those.
-    //
     // Padded form with lengths: the items of long sequences cost more (one key tile per 128 valid keys), so the
     // sequences are handed out by decreasing number of key tiles - a counting sort that every CTA's scheduler warp
     // repeats for itself (a few hundred warp instructions; skipped for batches where it would cost more).
@@ -417,326 +443,181 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       ++n;
       if (k.n_kv < 0) break;
     }
-  } else if (warp == W_BAND) {
-    // ================================ MMA issuer: the two position bands =====================
-    // One thread: C(0) P2(0) C(1) P2(1) ... - the two bands of a key tile pass through the one band buffer in turn,
-    // each as soon as the drain warps have released it.  The same thread issues the bulk loads of the operands it
-    // consumes, at the moment it learns that their buffer is free (a drained band means that the product before it
-    // has retired): the Qr window and the K tile of key tile g when P2(g-1) has retired, the Kr window of tile g+1
-    // when C(g) has retired.  No separate producer has to notice the release first.
-    if (lane == 0 && (C2P || P2C)) {
+  } else if (warp == NCW + 1) {
+    // ================================ MMA issuer ============================================
+    if (lane == 0) {
+      constexpr uint32_t ID_S = make_idesc_bf16(128, BK, 0);
       constexpr uint32_t ID_BAND = make_idesc_bf16(128, BAND, 0);
       constexpr uint32_t ID_SAT = make_idesc_bf16(128, SATN, 0);
-      // operand descriptors of the four 16-wide slices of the head dimension, kept in registers: between two waits
-      // this thread then executes little more than the MMA instructions themselves
-      uint64_t dQ[2][HD / 16], dK[HD / 16], dKr[HD / 16], dQr[HD / 16];
-#pragma unroll
-      for (int k = 0; k < HD / 16; ++k) {
-        dQ[0][k] = smem_desc_sw128(sQ) + 2 * k;
-        dQ[1][k] = smem_desc_sw128(sQ + TILE_BYTES) + 2 * k;
-        dK[k] = smem_desc_sw128(sK) + 2 * k;
-        dKr[k] = smem_desc_sw128(sKr) + 2 * k;
-        dQr[k] = smem_desc_sw128(sQr) + 2 * k;
-      }
+      constexpr uint32_t ID_PV = make_idesc_bf16(128, HD, 1);
+      const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
+      const uint64_t dKr = smem_desc_sw128(sKr), dQr = smem_desc_sw128(sQr);
+      const uint32_t tS = tmem + TM_S, tO = tmem + TM_O, tP = tmem + TM_P;
       const uint32_t tBand = tmem + TM_RING;
-      // a position in the stream of key tiles, with what the loads of that tile need
-      struct Cur { int n, it, n_kv, q0, h, bcoord, valid; int64_t tok0; };
-      auto open_item = [&](Cur& c) {
+      int fills = 0;                       // how often the band buffer has been filled so far
+
+      // A position in this CTA's stream of key tiles: ring index of the work item, key tile inside it.
+      struct TileCur { int n, it, n_kv, q0; bool ok; };
+      auto cur_fetch = [&](TileCur& c) {
         Work k;
-        const bool ok = fetch(c.n, k);
-        release(c.n);
-        c.valid = ok; c.it = 0; c.n_kv = k.n_kv; c.q0 = k.q0; c.h = k.h; c.bcoord = k.bcoord; c.tok0 = k.tok0;
+        c.ok = fetch(c.n, k);
+        c.n_kv = k.n_kv; c.q0 = k.q0;
       };
-      auto advance = [&](Cur& c) {
-        if (!c.valid) return;
+      auto cur_next = [&](TileCur& c) {
         if (c.it + 1 < c.n_kv) { ++c.it; return; }
-        ++c.n;
-        open_item(c);
+        ++c.n; c.it = 0;
+        cur_fetch(c);
       };
-      auto load_table = [&](const Cur& c, bool kr) {
-        if (*abort_flag) return;
-        const int k0 = c.it * BK;
-        int x0 = c.q0 - k0 - (BK - 1) + p.exp_delta_max;
-        x0 = x0 < 0 ? 0 : (x0 > p.exp_rows - BAND ? p.exp_rows - BAND : x0);
-        const bool sat = LONG && tile_saturated(p, c.q0, k0);
-        mbar_expect_tx(bar(kr ? KR_FULL : QR_FULL), (sat ? SATN : BAND) * HD * 2);
-        tma_load_3d(kr ? sKr : sQr, kr ? (sat ? &tm_kr16 : &tm_kr) : (sat ? &tm_qr16 : &tm_qr), bar(kr ? KR_FULL : QR_FULL), 0, x0, c.h);
+      auto wait_q = [&](const TileCur& c) {                 // the item's Q tile has landed (once per item)
+        if (c.it == 0) wait(Q_FULL + (c.n & 1), (uint32_t)((c.n >> 1) & 1));
       };
-      auto load_k = [&](const Cur& c) {
-        if (*abort_flag) return;
-        mbar_expect_tx(bar(K_FULL), TILE_BYTES);
-        tma_load_4d(sK, &tm_k, bar(K_FULL), 0, (int)(c.tok0 + c.it * BK), c.h, c.bcoord);
+      auto wait_ring_free = [&]() {
+        if (fills > 0) wait(BAND_FREE, (uint32_t)((fills - 1) & 1));
       };
-      Cur cur, nxt;
-      cur.n = 0;
-      open_item(cur);
-      nxt = cur;
-      advance(nxt);
-      int fills = 0, g = 0;                // fills of the band buffer so far, key tiles so far
-      if (cur.valid && C2P) load_table(cur, true);
-      while (cur.valid) {
-        const uint32_t idesc = (LONG && tile_saturated(p, cur.q0, cur.it * BK)) ? ID_SAT : ID_BAND;
-        const int qb = cur.n & 1;
-        // the band product before this one has been drained, hence has retired: the buffers it read are free
-        auto band_free = [&]() { if (fills > 0) wait(BAND_FREE, (uint32_t)((fills - 1) & 1)); };
-        auto loads_after_p2 = [&]() {      // P2(g-1) has retired (or there was none): Qr window and K tile of this tile
-          if (P2C) {
-            load_table(cur, false);
-            if (g > 0) wait(K_EMPTY, (uint32_t)((g - 1) & 1));       // the score product of the previous tile as well
-            load_k(cur);
-          }
-        };
-        if (C2P) {
-          if (!P2C && g > 0) { band_free(); load_table(cur, true); }   // c2p only: C(g-1) has retired, this tile's window
-          wait(KR_FULL, (uint32_t)(g & 1));
-          if (cur.it == 0) wait(Q_FULL + qb, (uint32_t)((cur.n >> 1) & 1));
-          band_free();
-          loads_after_p2();
-          tc_fence_after();
-          if (qb) {
-            mma_ss<false>(tBand, dQ[1][0], dKr[0], idesc);
+      auto ring_filled = [&]() {
+        tc_commit(bar(BAND_FULL));
+        ++fills;
+      };
+      // content->position band of key tile g (global count): one 256-column product into the band buffer
+      auto issue_c = [&](const TileCur& c, int g) {
+        wait(KR_FULL, (uint32_t)(g & 1));
+        wait_q(c);
+        wait_ring_free();
+        tc_fence_after();
+        const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
+        const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-            for (int kk = 1; kk < HD / 16; ++kk) mma_ss<true>(tBand, dQ[1][kk], dKr[kk], idesc);
-          } else {
-            mma_ss<false>(tBand, dQ[0][0], dKr[0], idesc);
+        for (int k = 0; k < HD / 16; ++k) mma_ss_dyn(tBand, dQc + 2 * k, dKr + 2 * k, idesc, k > 0);
+        ring_filled();
+        tc_commit(bar(KR_EMPTY));
+      };
+      // content score of key tile g; the last one of an item releases the item's Q buffer
+      auto issue_s = [&](const TileCur& c, int g) {
+        wait(K_FULL, (uint32_t)(g & 1));
+        if (!C2P) wait_q(c);
+        if (g > 0) wait(S_TAKEN, (uint32_t)((g - 1) & 1));
+        tc_fence_after();
+        const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
 #pragma unroll
-            for (int kk = 1; kk < HD / 16; ++kk) mma_ss<true>(tBand, dQ[0][kk], dKr[kk], idesc);
-          }
-          tc_commit(bar(BAND_FULL));
-          ++fills;
-          if (cur.it + 1 == cur.n_kv) tc_commit(bar(Q_EMPTY + qb));
-        }
+        for (int k = 0; k < HD / 16; ++k) mma_ss_dyn(tS, dQc + 2 * k, dK + 2 * k, ID_S, k > 0);
+        tc_commit(bar(S_FULL));
+        if (c.it + 1 == c.n_kv) tc_commit(bar(Q_EMPTY + (c.n & 1)));
+      };
+      // position->content band of key tile g (rows = keys), once the c2p band has been drained; releases K
+      auto issue_p2 = [&](const TileCur& c, int g) {
         if (P2C) {
-          if (!C2P) { band_free(); loads_after_p2(); }               // p2c only: nothing else tells when P2(g-1) retired
           wait(QR_FULL, (uint32_t)(g & 1));
-          wait(K_FULL, (uint32_t)(g & 1));
-          band_free();
-          if (C2P && nxt.valid) load_table(nxt, true);                 // C(g) has retired: the next tile's Kr window
+          wait_ring_free();
           tc_fence_after();
-          mma_ss<false>(tBand, dK[0], dQr[0], idesc);
+          const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-          for (int kk = 1; kk < HD / 16; ++kk) mma_ss<true>(tBand, dK[kk], dQr[kk], idesc);
-          tc_commit(bar(BAND_FULL));
-          ++fills;
+          for (int k = 0; k < HD / 16; ++k) mma_ss_dyn(tBand, dK + 2 * k, dQr + 2 * k, idesc, k > 0);
+          ring_filled();
+          tc_commit(bar(QR_EMPTY));
         }
-        cur = nxt;
-        advance(nxt);
-        ++g;
+        tc_commit(bar(K_EMPTY));
+      };
+      // O += P . V of key tile g.  The first one of an item overwrites O: the CUDA warps read the previous item's O
+      // before they announce the P of this tile, so P_READY covers that as well.
+      auto issue_pv = [&](const TileCur& c, int g) {
+        wait(V_FULL, (uint32_t)(g & 1));
+        wait(P_READY, (uint32_t)(g & 1));
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          mma_ts_dyn(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (c.it > 0 || k > 0) ? 1u : 0u);
+        tc_commit(bar(O_FULL));
+        tc_commit(bar(V_EMPTY));
+      };
+
+      // Issue order: C(0) S(0) P2(0) C(1) | S(1) P2(1) C(2) PV(0) | S(2) P2(2) C(3) PV(1) | ...  so that the band of
+      // tile g+2 is under way as soon as the band buffer has been drained of tile g+1, well before the CUDA warps
+      // ask for it, and P.V of tile g never delays the scores of the tiles after it.
+      TileCur cc, cs, cv;                  // c2p stream (two tiles ahead), score/p2c stream (one ahead), P.V stream
+      cc.n = 0; cc.it = 0; cur_fetch(cc);
+      cs = cc; cv = cc;
+      int gc = 0, gs = 0, gv = 0;
+      if (cv.ok) {
+        if (C2P) { issue_c(cc, gc++); cur_next(cc); }
+        issue_s(cs, gs); issue_p2(cs, gs); ++gs;
+        if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
+        while (true) {
+          TileCur nx = cs;
+          cur_next(nx);
+          if (nx.ok) {
+            cs = nx;
+            issue_s(cs, gs); issue_p2(cs, gs); ++gs;
+            if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
+          }
+          issue_pv(cv, gv++);
+          if (cv.it + 1 == cv.n_kv) release(cv.n);
+          cur_next(cv);
+          if (!cv.ok) break;
+        }
       }
+      release(cv.n);                       // the end-of-stream marker
       // Everything issued above must have retired before tensor memory is released.
       tc_commit(bar(DONE));
       int never = 0;                       // this wait runs even after an abort, with its own limit
       mbar_wait(bar(DONE), 0, &never, p.status, 1 + DONE, WAIT_LIMIT_NS);
-    } else if (lane == 0) {
-      int n = 0;                           // no position terms: only the work ring counts this lane among its readers
-      Work k;
-      while (true) { const bool ok = fetch(n, k); release(n); if (!ok) break; ++n; }
     }
-  } else if (warp == W_SPV) {
-    // ================================ MMA issuer: scores and P.V =============================
-    // One thread: S(0) | S(1) PV(0) | S(2) PV(1) | ...  The score product of the next key tile goes out as soon as
-    // the softmax warps have taken the previous scores out of tensor memory; P.V of a tile follows when they have
-    // stored its probabilities.  The first P.V of an item overwrites O: the softmax warps read the previous item's O
-    // before they announce the P of this tile, so P_READY covers that as well.
-    // Only the 16-key blocks that hold valid keys are multiplied, and the V rows between the last valid key and the
-    // end of its block are zeroed first: the probabilities there are exact zeros, but what the caller left in the
-    // padding of V need not be finite, and 0 x NaN would reach every query row of the tile.
-    // This thread also issues the bulk loads of Q (the next item's tile, when the buffer it goes to has been
-    // released), of V (this tile's, when the P.V before it has retired) and - without a position->content term, when
-    // the band lane does not do it - of K.
-    if (lane == 0) {
-      constexpr uint32_t ID_S = make_idesc_bf16(128, BK, 0);
-      constexpr uint32_t ID_PV = make_idesc_bf16(128, HD, 1);
-      uint64_t dQ[2][HD / 16], dK[HD / 16], dV[BK / 16];
-#pragma unroll
-      for (int k = 0; k < HD / 16; ++k) {
-        dQ[0][k] = smem_desc_sw128(sQ) + 2 * k;
-        dQ[1][k] = smem_desc_sw128(sQ + TILE_BYTES) + 2 * k;
-        dK[k] = smem_desc_sw128(sK) + 2 * k;
-      }
-#pragma unroll
-      for (int kk = 0; kk < BK / 16; ++kk) dV[kk] = smem_desc_sw128(sV) + (uint64_t)(128 * kk);
-      const uint32_t tS = tmem + TM_S, tO = tmem + TM_O, tP = tmem + TM_P;
-      // the P.V of the tile before the current one is described by (pv_it, pv_nvalid); pv_it < 0: none pending
-      int n = 0, g = 0, pv_it = -1, pv_nvalid = 0;
-      auto issue_pv = [&](int gp) {        // P.V of key tile gp (stream count)
-        wait(V_FULL, (uint32_t)(gp & 1));
-        int kblocks = BK / 16;
-        if (pv_nvalid < BK) {
-          kblocks = (pv_nvalid + 15) >> 4;
-          for (int r = pv_nvalid; r < kblocks * 16; ++r)
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) sts_128(sV + (uint32_t)r * 128u + 16u * ch, 0u, 0u, 0u, 0u);
-          fence_proxy_async_smem();
-        }
-        wait(P_READY, (uint32_t)(gp & 1));
-        tc_fence_after();
-        if (kblocks == BK / 16 && pv_it > 0) {                       // the common case: eight instructions and nothing else
-#pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) mma_ts<true>(tO, tP + 8 * kk, dV[kk], ID_PV);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk)
-            if (kk < kblocks) mma_ts_dyn(tO, tP + 8 * kk, dV[kk], ID_PV, (pv_it > 0 || kk > 0) ? 1u : 0u);
-        }
-        tc_commit(bar(O_FULL));
-        tc_commit(bar(V_EMPTY));
-      };
-      auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int full, const Work& w, int row) {
-        if (*abort_flag) return;
-        mbar_expect_tx(bar(full), TILE_BYTES);
-        tma_load_4d(dst, tm, bar(full), 0, (int)(w.tok0 + row), w.h, w.bcoord);
-      };
-      Work k, kn;                          // this item and the one after it
-      bool ok = fetch(0, k);
-      release(0);
-      bool okn = false;
-      if (ok) {
-        load_tile(sQ, &tm_q, Q_FULL, k, k.q0);
-        if (!P2C) load_tile(sK, &tm_k, K_FULL, k, 0);
-        load_tile(sV, &tm_v, V_FULL, k, 0);
-        okn = fetch(1, kn);
-        release(1);
-      }
-      while (ok) {
-        const int qb = n & 1;
-        for (int it = 0; it < k.n_kv; ++it, ++g) {
-          wait(K_FULL, (uint32_t)(g & 1));
-          if (it == 0) wait(Q_FULL + qb, (uint32_t)((n >> 1) & 1));
-          if (g > 0) wait(S_TAKEN, (uint32_t)((g - 1) & 1));
-          tc_fence_after();
-          if (qb) {
-            mma_ss<false>(tS, dQ[1][0], dK[0], ID_S);
-#pragma unroll
-            for (int kk = 1; kk < HD / 16; ++kk) mma_ss<true>(tS, dQ[1][kk], dK[kk], ID_S);
-          } else {
-            mma_ss<false>(tS, dQ[0][0], dK[0], ID_S);
-#pragma unroll
-            for (int kk = 1; kk < HD / 16; ++kk) mma_ss<true>(tS, dQ[0][kk], dK[kk], ID_S);
-          }
-          tc_commit(bar(S_FULL));
-          tc_commit(bar(K_EMPTY));
-          if (it + 1 == k.n_kv) tc_commit(bar(Q_EMPTY + qb));
-          if (it == 0 && okn) {            // the next item's Q tile, into the buffer that the item before this one used
-            if (n >= 1) wait(Q_EMPTY + (qb ^ 1), (uint32_t)(((n - 1) >> 1) & 1));
-            load_tile(sQ + (uint32_t)(qb ^ 1) * TILE_BYTES, &tm_q, Q_FULL + (qb ^ 1), kn, kn.q0);
-          }
-          if (pv_it >= 0) {
-            issue_pv(g - 1);
-            wait(V_EMPTY, (uint32_t)((g - 1) & 1));                    // that product has retired: this tile's V may come in
-          }
-          if (g > 0) load_tile(sV, &tm_v, V_FULL, k, it * BK);
-          if (!P2C) {                      // K of the next key tile, once this tile's scores have retired
-            const bool more = it + 1 < k.n_kv;
-            if (more || okn) {
-              wait(K_EMPTY, (uint32_t)(g & 1));
-              if (more) load_tile(sK, &tm_k, K_FULL, k, (it + 1) * BK);
-              else load_tile(sK, &tm_k, K_FULL, kn, 0);
-            }
-          }
-          pv_it = it; pv_nvalid = k.len - it * BK;
-        }
-        ++n;
-        k = kn; ok = okn;
-        if (ok) { okn = fetch(n + 1, kn); release(n + 1); }
-      }
-      if (pv_it >= 0) issue_pv(g - 1);
-      tc_commit(bar(DONE_PV));
-      int never = 0;
-      mbar_wait(bar(DONE_PV), 0, &never, p.status, 1 + DONE_PV, WAIT_LIMIT_NS);
-    }
-  } else if (warp >= W_DRAIN && warp < W_DRAIN + NDW) {
-    // ================================ band drains ============================================
-    // Warp d owns tensor-memory lanes 32*d..+31: query rows of the c2p band, key rows of the p2c band.  Per key tile:
-    // band buffer full -> staging rows of the previous tile released by their readers -> copy -> band buffer free,
-    // staging rows full.
-    if (C2P || P2C) {
-      const int qd = warp & 3, part = (warp - W_DRAIN) >> 2;          // quadrant of rows, share of the columns
-      const int row = qd * 32 + lane;
-      const uint32_t lane_base = ((uint32_t)(qd * 32)) << 16;
-      // staging rows: c2p row i holds band columns [32*qd, +160); p2c row j holds band columns [96 - 32*qd, +160).
-      // c2p rows are laid out in pairs (656 bytes per pair, the odd row 320 bytes in): 16-byte row stores of a warp
-      // hit eight different 16-byte slots, and the skewed 32-bit reads (one row per lane, two bytes further per
-      // lane) hit 32 different banks.
-      const uint32_t c_row = stC + (uint32_t)(row >> 1) * 656u + (uint32_t)(row & 1) * 320u;
-      const uint32_t p_row = stP + (uint32_t)row * STG_STRIDE;
-      int n = 0, g = 0, drains = 0;
-      while (true) {
-        int n_kv = -1, q0 = 0;
-        if (lane == 0) {
-          Work k;
-          if (fetch(n, k)) { n_kv = k.n_kv; q0 = k.q0; }
-          release(n);
-        }
-        n_kv = __shfl_sync(0xffffffffu, n_kv, 0);
-        q0 = __shfl_sync(0xffffffffu, q0, 0);
-        if (n_kv <= 0) break;
-        for (int it = 0; it < n_kv; ++it, ++g) {
-          const bool sat = LONG && tile_saturated(p, q0, it * BK);
-#pragma unroll
-          for (int kind = 0; kind < 2; ++kind) {
-            if (kind == 0 ? !C2P : !P2C) continue;
-            wait(BAND_FULL, (uint32_t)(drains & 1));
-            ++drains;
-            if (g > 0) wait((kind == 0 ? STC_FREE0 : STP_FREE0) + qd, (uint32_t)((g - 1) & 1));
-            tc_fence_after();
-            if (sat) {                                                   // one value per row: column 0 of the band
-              if (part == 0) {
-                uint32_t r[16];
-                tmem_ld_cols<16>(tmem + lane_base + TM_RING, r);
-                sts_f32((kind == 0 ? satC : satP) + 4u * (uint32_t)row, __uint_as_float(r[0]));
-              }
-            } else if (kind == 0) {
-              drain_band_row<DRAIN_COLS>(tmem + lane_base + TM_RING + (uint32_t)(32 * qd + DRAIN_COLS * part),
-                                         c_row + 2u * (uint32_t)(DRAIN_COLS * part));
-            } else {
-              drain_band_row<DRAIN_COLS>(tmem + lane_base + TM_RING + (uint32_t)(96 - 32 * qd + DRAIN_COLS * part),
-                                         p_row + 2u * (uint32_t)(DRAIN_COLS * part));
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              mbar_arrive(bar(BAND_FREE));
-              mbar_arrive(bar((kind == 0 ? STC_FULL0 : STP_FULL0) + qd));
-            }
-          }
-        }
-        ++n;
-      }
-    } else {
-      // no position terms: nothing to drain, but the work ring still counts this warp among its readers
-      int n = 0;
-      while (true) {
-        int n_kv = -1;
-        if (lane == 0) {
-          Work k;
-          if (fetch(n, k)) n_kv = k.n_kv;
-          release(n);
-        }
-        n_kv = __shfl_sync(0xffffffffu, n_kv, 0);
-        if (n_kv <= 0) break;
-        ++n;
-      }
-    }
-  } else if (warp < NSW) {
-    // ================================ softmax + epilogue =====================================
+  } else {
+    // ================================ drain + softmax + epilogue ============================
     const int qd = warp & 3, grp = warp >> 2;
-    const int row_t = qd * 32 + lane;                                  // tensor-memory lane = query row
+    const int row_t = qd * 32 + lane;                                  // tensor-memory lane = query row (or key row of P2)
     const uint32_t lane_base = ((uint32_t)(qd * 32)) << 16;
     const uint32_t tS = tmem + lane_base + TM_S + KPT * grp;
     const uint32_t tO = tmem + lane_base + TM_O + OPT * grp;
     const uint32_t tP = tmem + lane_base + TM_P + (KPT / 2) * grp;
     const float sl2 = p.sm_scale * 1.4426950408889634f;
+    // staging rows: c2p row i holds band columns [32*qd, +160); p2c row j holds band columns [96 - 32*(j/32), +160)
+    // c2p rows are laid out in pairs (656 bytes per pair, the odd row 320 bytes in): 16-byte row stores of a warp
+    // hit eight different 16-byte slots, and the skewed 32-bit reads (one row per lane, two bytes further per
+    // lane) hit 32 different banks.
     const uint32_t c_row = stC + (uint32_t)(row_t >> 1) * 656u + (uint32_t)(row_t & 1) * 320u;
+    const uint32_t p_row = stP + (uint32_t)row_t * STG_STRIDE;
     const uint32_t c_read = c_row + 2u * (uint32_t)(lane + (BK - 1) - KPT * grp);          // key e of this thread: c_read - 2e
     const uint32_t p_read = stP + (uint32_t)(KPT * grp) * STG_STRIDE + 2u * (uint32_t)(row_t + 31);  // + e*STRIDE - 2*(e%32)
     const uint32_t x_mine = sX + 4u * (uint32_t)(grp * BQ + row_t);
+    int drains = 0;
 
-    // The softmax warps walk one flat stream of key tiles.  Thread 0 copies the work items from the scheduler's
+    // Drain the band buffer into this warp's share of the staging rows.  kind 0: c2p (window starts at 32*qd),
+    // kind 1: p2c (96 - 32*qd).
+    auto drain_band = [&](int kind, bool sat) {
+      wait(BAND_FULL, (uint32_t)(drains & 1));
+      ++drains;
+      tc_fence_after();
+      if (sat) {                                                       // one value per row: column 0 of the band
+        if (grp == 0) {
+          uint32_t r[16];
+          tmem_ld_cols<16>(tmem + lane_base + TM_RING, r);
+          sts_f32(kind == 0 ? c_row : stP + 4u * (uint32_t)row_t, __uint_as_float(r[0]));
+        }
+      } else {
+        // The 160 staged columns of a row are split evenly over the four warps that own the row: 40 columns each.
+        const int local = (STG_COLS / GROUPS) * grp;                   // position inside the staging row
+        const uint32_t src = tmem + lane_base + TM_RING + (uint32_t)((kind == 0 ? 32 * qd : 96 - 32 * qd) + local);
+        const uint32_t dst = (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local;
+        drain_chunk(src, dst);
+        uint32_t r[8];
+        tmem_ld8(src + 32, r);
+        tmem_ld_wait8(r);
+        sts_128(dst + 64, pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+                pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+                pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAND_FREE));
+    };
+    auto drain_c = [&](bool sat) { if (C2P) drain_band(0, sat); };
+    auto drain_p2 = [&](bool sat) { if (P2C) drain_band(1, sat); };
+
+    // The CUDA-core warps walk one flat stream of key tiles.  Thread 0 copies the work items from the scheduler's
     // ring into four slots, two items ahead of the one being processed, so that every warp takes its trip counts
     // from the same copy (also after an abort) and an item switch needs no extra barrier: a slot is written at
-    // least one barrier of all softmax warps before anybody reads it, and rewritten only after its last reader has
-    // passed one.
+    // least one CTA-wide barrier before anybody reads it, and rewritten only after its last reader has passed one.
     static_assert(sizeof(Work) == 32, "work items are copied as two 16-byte vectors");
     const uint32_t slots = sbase + OFF_CUR + 16;                       // four items of 32 bytes
     volatile Work* const item_slots = reinterpret_cast<volatile Work*>(gbase + OFF_CUR + 16);
@@ -777,29 +658,42 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       tc_fence_before();
       float inv;
       asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(l_tot));
-      // Each thread owns 16 consecutive output columns of its row: two 16-byte stores (whole 32-byte sectors).
+      // The normalised rows go through shared memory (the quadrant's part of the p2c staging area, which nobody
+      // uses between the barrier that closed this tile's p2c reads and the next drain) so that each store
+      // instruction writes four whole 128-byte rows instead of 32 separate 16-byte pieces.
       {
         const bool valid = w.q0 + row_t < w.len;
         uint32_t outw[OPT / 2];
 #pragma unroll
         for (int e = 0; e < OPT; e += 2)
           outw[e / 2] = valid ? pack_bf16x2(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv) : 0u;
-        const int row = w.q0 + row_t;
-        if (row < w.rows) {
-          __nv_bfloat16* const orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)w.bcoord * p.o_sb +
-                                      (int64_t)w.h * p.o_sh + (w.tok0 + row) * p.o_st + OPT * grp;
+        const uint32_t obuf = stP + (uint32_t)(32 * qd) * STG_STRIDE;          // 32 rows, 144-byte pitch
+        const uint32_t mine = obuf + (uint32_t)lane * 144u + (uint32_t)(OPT * 2 * grp);
 #pragma unroll
-          for (int i = 0; i < OPT / 8; ++i)
-            *reinterpret_cast<uint4*>(orow + 8 * i) = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
-          if (p.lse && grp == 0)
+        for (int i = 0; i < OPT / 8; ++i)
+          sts_128(mine + 16u * i, outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
+        bar_quadrant(qd);
+        __nv_bfloat16* const obase = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)w.bcoord * p.o_sb +
+                                     (int64_t)w.h * p.o_sh + 8 * (lane & 7);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int rq = 8 * grp + 4 * i + (lane >> 3);                        // row inside the quadrant
+          const int row = w.q0 + 32 * qd + rq;
+          const uint4 v = lds_128(obuf + (uint32_t)rq * 144u + 16u * (uint32_t)(lane & 7));
+          if (row < w.rows) *reinterpret_cast<uint4*>(obase + (w.tok0 + row) * p.o_st) = v;
+        }
+        if (p.lse && grp == 0) {
+          const int row = w.q0 + row_t;
+          if (row < w.rows)
             p.lse[(int64_t)w.bcoord * p.lse_sb + (int64_t)w.h * p.lse_sh + w.tok0 + row] =
                 valid ? (lds_f32(mx_row + par * (BQ * 4)) * 0.6931471805599453f + logf(l_tot)) : 0.f;
         }
+        bar_quadrant(qd);                                                      // the staging rows may be drained into again
       }
     };
 
     if (tid == 0) { leader_publish(0); leader_publish(1); }
-    bar_softmax_warps();
+    bar_all_cuda_warps();
     struct { int q0, len, n_kv; } cur;
     auto switch_item = [&](int n) {
       volatile Work* w = item_slots + (n & 3);
@@ -808,30 +702,40 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     switch_item(0);
     if (cur.n_kv > 0) {
       if (tid == 0) leader_publish(2);
+      {                                                                // bands of the very first key tile
+        const bool sat0 = LONG && tile_saturated(p, cur.q0, 0);
+        drain_c(sat0);
+        drain_p2(sat0);
+        bar_all_cuda_warps();
+      }
       float m_run = 0.f, l_part = 0.f;
       int n = 0, it = 0, g = 0;
       while (true) {
         const bool last_of_item = (it + 1 == cur.n_kv);
+        const bool has_next = !last_of_item || item_slots[(n + 1) & 3].n_kv > 0;
         const int nvalid = cur.len - it * BK - KPT * grp;            // keys e >= nvalid of this thread are masked
-        const bool sat = LONG && tile_saturated(p, cur.q0, it * BK);
+        const bool sat = LONG && tile_saturated(p, cur.q0, it * BK);   // this key tile, and the one after it
+        const bool sat_n = LONG && (!last_of_item ? tile_saturated(p, cur.q0, (it + 1) * BK)
+                                                  : tile_saturated(p, item_slots[(n + 1) & 3].q0, 0));
         wait(S_FULL, (uint32_t)(g & 1));
         tc_fence_after();
         float s[KPT];
-        tmem_ld_cols<KPT>(tS, reinterpret_cast<uint32_t*>(s));
+        {
+          tmem_ld_cols<KPT>(tS, reinterpret_cast<uint32_t*>(s));
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(S_TAKEN));
-        // Phase 1: add the content->position term from this thread's own staging row, then hand the rows of the
-        // quadrant back to its drain warp.
+        // Phase 1: add the content->position term, then hand the c2p staging rows (shared only inside the
+        // quadrant) to the next key tile at once, so that its position->content products can run during phase 2.
         if (C2P) {
-          wait(STC_FULL0 + qd, (uint32_t)(g & 1));
+          // The 32 values sit at descending addresses from c_read; read them as 17 aligned 32-bit words and
+          // realign odd lanes with a funnel shift (half the shared-memory wavefronts of 16-bit loads).
           if (sat) {
-            const float cq = lds_f32(satC + 4u * (uint32_t)row_t);
+            const float cq = lds_f32(c_row);
 #pragma unroll
             for (int e = 0; e < KPT; ++e) s[e] += cq;
           } else {
-            // The 32 values sit at descending addresses from c_read; read them as 17 aligned 32-bit words and
-            // realign odd lanes with a funnel shift (half the shared-memory wavefronts of 16-bit loads).
             const uint32_t lo_addr = (c_read - 2u * (KPT - 1)) & ~3u;
             const uint32_t sh = (uint32_t)(lane & 1) * 16u;
             uint32_t wv[KPT / 2 + 1];
@@ -840,11 +744,14 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
 #pragma unroll
             for (int k = 0; k < KPT / 2; ++k) {
               const uint32_t v = __funnelshift_r(wv[k], wv[k + 1], sh);       // (element 2k, element 2k+1) ascending
-              add_bf16x2(s[KPT - 1 - 2 * k], s[KPT - 2 - 2 * k], v);
+              uint16_t lo, hi;
+              asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(v));
+              s[KPT - 1 - 2 * k] = add_bf16(s[KPT - 1 - 2 * k], lo);
+              s[KPT - 2 - 2 * k] = add_bf16(s[KPT - 2 - 2 * k], hi);
             }
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(STC_FREE0 + qd));
+          bar_quadrant(qd);
+          if (has_next) drain_c(sat_n);
         }
         // Phase 2.  Scores stay unscaled in s[]; the exponentials are taken at once against the reference exponent
         // of the previous tiles (0 on the first tile) so that the MUFU work overlaps the shared-memory reads, and
@@ -852,16 +759,16 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const float m_prev = (it > 0) ? m_run : 0.f;
         float lsum = 0.f;
         uint32_t pk[KPT / 2];
-        if (P2C) wait(STP_FULL0 + grp, (uint32_t)(g & 1));
         if (sat) {
-          // Saturated tile: p2c is one value per key; masking is applied unconditionally, this path is not the common one.
+          // Saturated tile: p2c is one value per key (floats at the start of the p2c staging area); masking is
+          // applied unconditionally, this path is not the common one.
           if (P2C) {
 #pragma unroll
             for (int v = 0; v < KPT / 4; ++v) {
               float4 t;
               asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                            : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w)
-                           : "r"(satP + 4u * (uint32_t)(KPT * grp + 4 * v)));
+                           : "r"(stP + 4u * (uint32_t)(KPT * grp + 4 * v)));
               s[4 * v] += t.x; s[4 * v + 1] += t.y; s[4 * v + 2] += t.z; s[4 * v + 3] += t.w;
             }
           }
@@ -903,26 +810,20 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             pk[e / 2] = pack_bf16x2(a, b);
           }
         }
-        if (P2C) {                                                     // the key rows of this group go back to their drain warp
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(STP_FREE0 + grp));
-        }
-        // The barrier below carries a vote: only when some thread of the CTA saw a score far from the reference
-        // exponent do the rows exchange their maxima and move the exponent; otherwise it simply stays.
+        // The barrier below closes the reads of the p2c staging rows of this key tile (so the next tile's band can
+        // be drained into them) and carries a vote: only when some thread of the CTA saw a score far from the
+        // reference exponent do the rows exchange their maxima and move the exponent; otherwise it simply stays.
         // The vote reads the row sums: an exponential above 2^8 (or an overflow) shows as a large sum, a first tile
         // far below the exponent as a vanishing one.  The maxima themselves are only formed when the vote passes.
         const bool vote = (lsum > 256.f) || (it == 0 && nvalid > 0 && lsum < 1.7e-18f);
-        const bool moved = bar_softmax_warps_or(vote);
-        // Every thread has now finished with the slot of item n - 2 (its epilogue ran in the first tile of item
-        // n - 1): the leader may reuse it for item n + 2.
-        if (tid == 0 && it == 0 && n > 0) leader_publish(n + 2);
+        const bool moved = bar_all_cuda_warps_or(vote);
         float m_new = m_prev, alpha = 1.f;
         if (moved) {
           float mx = -CUDART_INF_F;
 #pragma unroll
           for (int e = 0; e < KPT; ++e) mx = fmaxf(mx, s[e]);
           sts_f32(x_mine, mx);
-          bar_softmax_warps();
+          bar_all_cuda_warps();
 #pragma unroll
           for (int gg = 0; gg < GROUPS; ++gg) mx = fmaxf(mx, lds_f32(sX + 4u * (uint32_t)(gg * BQ + row_t)));
           const float row_max = mx * sl2;                              // sl2 > 0
@@ -960,18 +861,20 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_READY));
+        if (has_next) drain_p2(sat_n);                                 // p2c staging rows are free since the barrier above
         if (last_of_item) {                                            // what the item's epilogue needs from this thread
           sts_f32(lx_mine + (uint32_t)(n & 1) * (GROUPS * BQ * 4), l_part);
           if (grp == 0) sts_f32(mx_row + (uint32_t)(n & 1) * (BQ * 4), m_run);
         }
+        bar_all_cuda_warps();                                          // next tile's staging complete; exchange buffer free
         ++g;
         if (!last_of_item) { ++it; continue; }
         ++n;
         it = 0;
         switch_item(n);
         if (cur.n_kv <= 0) break;
+        if (tid == 0) leader_publish(n + 2);
       }
-      bar_softmax_warps();                 // the last item's row sums are visible to every warp of its rows
       finish_item(n - 1, g - 1);
     }
   }
@@ -984,7 +887,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == W_BAND) tmem_dealloc(tmem, TM_COLS);
+  if (warp == NCW + 1) tmem_dealloc(tmem, TM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1079,6 +982,7 @@ int static_tile_scratch(void** ptr) {
   return TDB_OK;
 }
 
+
 size_t umma_workspace_bytes(int n_seqs, int64_t total_tokens) {
   int64_t cap = (total_tokens + BQ - 1) / BQ + n_seqs + 1;
   return sizeof(TileListHeader) + (size_t)cap * sizeof(int2);
@@ -1103,7 +1007,7 @@ int launch_attn_umma(const AttnParams& p, cudaStream_t s) {
     if ((rc = table_map(&maps[6], p.qr_exp, p.exp_rows, p.H, SATN, "qr_exp (saturated tiles)"))) return rc;
   } else { maps[4] = maps[0]; maps[6] = maps[0]; }
 
-  // Persistent CTAs: one per SM (most of its shared memory and all 512 tensor-memory columns each), never more
+  // Persistent CTAs: one per SM (201 KB of shared memory and all 512 tensor-memory columns each), never more
   // than there are work items (query tiles x heads).
   int dev = 0, sms = 0;
   if ((rc = cuda_fail(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
