@@ -233,3 +233,31 @@ def test_umma_repeated_runs_are_bitwise_identical():
     for _ in range(5):
         again = flash_attention_with_disentangled(*args, seqlens=lens, tables=tables, kernel=UMMA)
         assert torch.equal(first, again)
+
+
+def test_padding_of_k_and_v_may_hold_anything():
+    """Rows of K and V at or beyond a sequence's length are padding: the caller may leave NaN or infinities there.
+    The probabilities of those keys are exact zeros, but 0 x NaN is NaN, so the kernel must not let those rows into the
+    P.V product: results on the valid rows equal those with clean padding, bit for bit, in both kernels."""
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    w = _wl([200, 77, 129, 1], 256)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    lens = torch.as_tensor(np.asarray(w.lengths), dtype=torch.int32, device="cuda")
+    scale = 1.0 / (3 * 64) ** 0.5
+    run = lambda kk, vv, kern: flash_attention_with_disentangled(
+        q.permute(0, 2, 1, 3), kk.permute(0, 2, 1, 3), vv.permute(0, 2, 1, 3), None, None, False, scale, 256, 512,
+        seqlens=lens, tables=tables, kernel=kern).permute(0, 2, 1, 3)
+    kd, vd = k.clone(), v.clone()
+    for b, n in enumerate(w.lengths):
+        kd[b, n:] = float("nan")
+        vd[b, n:] = float("nan")
+        if n + 3 < 256:
+            vd[b, n + 1] = float("inf")
+            kd[b, n + 2] = float("-inf")
+    for kern in (UMMA, SIMT):
+        clean, dirty = run(k, v, kern), run(kd, vd, kern)
+        assert torch.isfinite(dirty.float()).all()
+        assert torch.equal(clean, dirty)
+    ref = util.oracle_fixed(q, k, v, tables, w.lengths, w, True, True, scale)
+    util.assert_close(run(kd, vd, UMMA), ref, DT, "dirty padding")

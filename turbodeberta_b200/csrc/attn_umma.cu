@@ -20,7 +20,8 @@
 // of the 128 keys, which puts four warps on every scheduler to hide latency.  Warp 16 = TMA producers (lane 0:
 // tables and K, lane 1: V, lane 2: Q), warp 17 = tensor-memory allocation + MMA issue (one lane), warp 18 =
 // scheduler (draws work items from a device-wide counter, publishes them in a shared-memory ring, zeroes tiles
-// that consist of padded rows only).
+// that consist of padded rows only; in the padded form it hands the sequences out longest first, so that the items
+// with the most key tiles are not the ones that finish last).
 //
 // Pipeline: the MMA lane issues C(0) S(0) P2(0) C(1) | S(g+1) P2(g+1) C(g+2) PV(g) | ..., so the bands and scores
 // of the next key tiles are produced while the CUDA warps work on tile g; C and P2 of a tile pass through the one
@@ -34,6 +35,10 @@
 // word, after which every role runs out its loops without waiting (the CUDA warps take their trip counts from
 // one copy of the work items kept by thread 0, so their named barriers still match), tensor memory is freed, and
 // the host reports TDB_ERR_TIMEOUT.
+//
+// Rows of K and V beyond a sequence's length are padding and may hold anything: their scores are replaced (not
+// multiplied) by -inf, and the softmax threads zero those rows of the V tile in shared memory before the P.V product
+// (an exact-zero probability times a NaN would otherwise reach every query row of the tile).
 //
 // Tensor-memory columns: [0,128) S, [128,192) O, [192,448) band buffer, [448,512) P (bf16).
 #include "tdb_internal.h"
@@ -158,6 +163,8 @@ __device__ __forceinline__ uint4 lds_128(uint32_t addr) {
 __device__ __forceinline__ void sts_128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// Makes this thread's earlier shared-memory writes visible to the asynchronous proxy (the tensor cores' operand fetch).
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void bar_all_cuda_warps() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 // The same barrier with an OR-reduction of one predicate per thread.
 __device__ __forceinline__ bool bar_all_cuda_warps_or(bool flag) {
@@ -853,6 +860,19 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           }
         } else if (n > 0) {
           finish_item(n - 1, g - 1);       // also frees O and P for this tile's P.V (announced by P_READY below)
+        }
+        // A key tile with fewer than 128 valid keys: the probabilities of the keys beyond the sequence are exact zeros,
+        // but what the caller left in the padding of V need not be finite, and 0 x NaN would reach every query row
+        // of the tile.  The softmax threads zero those rows of the V tile (it has landed long ago) before they
+        // announce P; the announcement orders the zeros before the product reads them.
+        {
+          const int nv_tile = cur.len - it * BK;
+          if (nv_tile < BK) {
+            wait(V_FULL, (uint32_t)(g & 1));
+            for (int idx = tid; idx < (BK - nv_tile) * 8; idx += NCT)
+              sts_128(sV + (uint32_t)(nv_tile + (idx >> 3)) * 128u + 16u * (uint32_t)(idx & 7), 0u, 0u, 0u, 0u);
+            fence_proxy_async_smem();
+          }
         }
         l_part = (it > 0 ? l_part * alpha : 0.f) + lsum;
         m_run = m_new;
