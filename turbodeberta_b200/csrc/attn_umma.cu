@@ -494,7 +494,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
         const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss_dyn(tBand, dQc + 2 * k, dKr + 2 * k, idesc, k > 0);
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dQc + 2 * k, dKr + 2 * k, idesc, k > 0);
         ring_filled();
         tc_commit(bar(KR_EMPTY));
       };
@@ -506,7 +506,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_fence_after();
         const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss_dyn(tS, dQc + 2 * k, dK + 2 * k, ID_S, k > 0);
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQc + 2 * k, dK + 2 * k, ID_S, k > 0);
         tc_commit(bar(S_FULL));
         if (c.it + 1 == c.n_kv) tc_commit(bar(Q_EMPTY + (c.n & 1)));
       };
@@ -518,7 +518,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           tc_fence_after();
           const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss_dyn(tBand, dK + 2 * k, dQr + 2 * k, idesc, k > 0);
+          for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dK + 2 * k, dQr + 2 * k, idesc, k > 0);
           ring_filled();
           tc_commit(bar(QR_EMPTY));
         }
@@ -532,7 +532,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
-          mma_ts_dyn(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (c.it > 0 || k > 0) ? 1u : 0u);
+          mma_ts(tO, tP + 8 * k, dV + (uint64_t)(128 * k), ID_PV, (c.it > 0 || k > 0) ? 1u : 0u);
         tc_commit(bar(O_FULL));
         tc_commit(bar(V_EMPTY));
       };

@@ -80,7 +80,7 @@ relpos_project_umma_kernel(const __grid_constant__ CUtensorMap tm_rel, const __g
         tc_fence_after();
         const uint64_t dA = smem_desc_sw128(sbase + s * STAGE_BYTES), dB = smem_desc_sw128(sbase + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
-        for (int k = 0; k < PK / 16; ++k) mma_ss_dyn(tmem, dA + 2 * k, dB + 2 * k, IDESC, (kc > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < PK / 16; ++k) mma_ss(tmem, dA + 2 * k, dB + 2 * k, IDESC, (kc > 0 || k > 0) ? 1u : 0u);
         tc_commit(bar(STAGES + s));        // the stage may be refilled once these products have read it
       }
       tc_commit(bar(2 * STAGES));          // accumulator complete
