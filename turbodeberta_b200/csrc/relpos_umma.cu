@@ -9,6 +9,7 @@
 #include "tdb_internal.h"
 #include "ptx_sm100.cuh"
 #include <cudaTypedefs.h>
+#include <mutex>
 
 namespace tdb {
 using namespace ptx;
@@ -141,14 +142,15 @@ __global__ void __launch_bounds__(32, 1) bounded_wait_selftest_kernel(int32_t* s
 }
 
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (!fn) {
+  // looked up once; a function-local static's initialisation is safe against concurrent first calls
+  static const PFN_cuTensorMapEncodeTiled_v12000 fn = []() -> PFN_cuTensorMapEncodeTiled_v12000 {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
-  }
+      return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    return nullptr;
+  }();
   return fn;
 }
 
@@ -180,13 +182,17 @@ int launch_relpos_project_umma(const void* rel, const void* W, const void* bias,
   int rc;
   if ((rc = map_2d(&tm_rel, rel, (uint64_t)hidden, (uint64_t)two_span, PM, "rel"))) return rc;
   if ((rc = map_2d(&tm_w, W, (uint64_t)hidden, (uint64_t)H * PN, PN, "W"))) return rc;
-  static int configured_dev = -1;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(relpos_project_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(relpos projection)");
-    configured_dev = dev;
+  {                                   // the shared-memory opt-in is a per-device attribute: set once per device
+    static std::mutex mu;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(relpos_project_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(relpos projection)");
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
   }
   dim3 grid((two_span + PM - 1) / PM, H);
   relpos_project_umma_kernel<<<grid, P_THREADS, P_SMEM, s>>>(tm_rel, tm_w, (const __nv_bfloat16*)bias, two_span, hidden, H,
