@@ -6,7 +6,8 @@
  * (paths are relative to src/turbodeberta/ of the reference).  All pointers are DEVICE pointers
  * unless stated otherwise; the library never allocates, frees or keeps device memory, launches on
  * the stream it is given and does not synchronise.  Every function returns TDB_OK (0) or a
- * negative TDB_ERR_* code; tdb_last_error() gives a thread-local detail string.
+ * negative TDB_ERR_* code; tdb_last_error() gives a thread-local detail string.  Entry points may be called
+ * from several host threads and for several devices at once.
  *
  * Element strides are in ELEMENTS of the tensor's dtype.  dtype: TDB_DTYPE_F32 or TDB_DTYPE_BF16.
  */
@@ -95,11 +96,13 @@ TDB_API size_t tdb_attn_workspace_bytes(int n_seqs, int64_t total_tokens);
  * [B,H,L,2*span] score tensors of that call are replaced by the projected tables kr/qr [H, two_span, D]
  * (the products are formed on chip), and `seqlens` adds the right-padding mask that the reference
  * kernel lacks.  q, k, v, o: logical shape [B, L, H, D], D contiguous, strides given per tensor.
- * seqlens: int32 [B] valid lengths or NULL (all L).  Query rows at or beyond the length are written as zeros.
+ * seqlens: int32 [B] valid lengths or NULL (all L).  Query rows at or beyond the length are written as zeros;
+ * rows of q, k, v at or beyond the length may hold anything (NaN included) and never reach the result.
  * idx: table from tdb_bucket_table; kr_exp/qr_exp: tables from tdb_relpos_expand (needed by the
  * tensor-core kernel; may be NULL for the CUDA-core kernel).  lse: float [B, H, L] or NULL.
  * status: int32[4] device words, zero on entry; word 0 becomes non-zero if a bounded wait gave up, word 1 if
- * cu_seqlens was malformed (packed form); word 2 is used by the tensor-core kernel as its work counter (the launch
+ * cu_seqlens was malformed (packed form: decreasing offsets, a sequence longer than max_seqlen, a last offset that
+ * differs from total_tokens); word 2 is used by the tensor-core kernel as its work counter (the launch
  * resets it), word 3 is reserved.  Do not share one status block between launches that can overlap. */
 TDB_API int tdb_attn_fwd_fixed(const void* q, const void* k, const void* v, void* o,
                        int64_t q_sb, int64_t q_st, int64_t q_sh,
