@@ -724,6 +724,10 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const bool sat = LONG && tile_saturated(p, cur.q0, it * BK);   // this key tile, and the one after it
         const bool sat_n = LONG && (!last_of_item ? tile_saturated(p, cur.q0, (it + 1) * BK)
                                                   : tile_saturated(p, item_slots[(n + 1) & 3].q0, 0));
+        // The next tile's c2p band is drained inside this tile's exponential loop (eight columns at a time between the
+        // loop's steps: that loop is bound by the special-function unit and has issue slots to spare, and the
+        // tensor-memory loads' latency disappears behind it); saturated tiles keep the separate one-value drain.
+        const bool fuse = C2P && has_next && !sat && !sat_n;
         wait(S_FULL, (uint32_t)(g & 1));
         tc_fence_after();
         float s[KPT];
@@ -758,7 +762,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             }
           }
           bar_quadrant(qd);
-          if (has_next) drain_c(sat_n);
+          if (has_next && !fuse) drain_c(sat_n);
         }
         // Phase 2.  Scores stay unscaled in s[]; the exponentials are taken at once against the reference exponent
         // of the previous tiles (0 on the first tile) so that the MUFU work overlaps the shared-memory reads, and
@@ -766,6 +770,31 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const float m_prev = (it > 0) ? m_run : 0.f;
         float lsum = 0.f;
         uint32_t pk[KPT / 2];
+        uint32_t dr[8];
+        const uint32_t d_src = tmem + lane_base + TM_RING + (uint32_t)(32 * qd + (STG_COLS / GROUPS) * grp);
+        const uint32_t d_dst = c_row + 2u * (uint32_t)((STG_COLS / GROUPS) * grp);
+        if (fuse) {
+          wait(BAND_FULL, (uint32_t)(drains & 1));
+          ++drains;
+          tc_fence_after();
+          tmem_ld8(d_src, dr);
+        }
+        // step c (0..4) of the fused drain: store the eight columns that have arrived, ask for the next eight; the
+        // band buffer is handed back as soon as the last load has completed
+        auto drain_step = [&](int c) {
+          tmem_ld_wait8(dr);
+          sts_128(d_dst + 16u * (uint32_t)c, pack_bf16x2(__uint_as_float(dr[0]), __uint_as_float(dr[1])),
+                  pack_bf16x2(__uint_as_float(dr[2]), __uint_as_float(dr[3])),
+                  pack_bf16x2(__uint_as_float(dr[4]), __uint_as_float(dr[5])),
+                  pack_bf16x2(__uint_as_float(dr[6]), __uint_as_float(dr[7])));
+          if (c + 1 < STG_COLS / GROUPS / 8) {
+            tmem_ld8(d_src + 8u * (uint32_t)(c + 1), dr);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAND_FREE));
+          }
+        };
         if (sat) {
           // Saturated tile: p2c is one value per key (floats at the start of the p2c staging area); masking is
           // applied unconditionally, this path is not the common one.
@@ -800,6 +829,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
+            if (((e / 2) & 1) && e / 4 < STG_COLS / GROUPS / 8 && fuse) drain_step(e / 4);
           }
         } else {
 #pragma unroll
@@ -815,6 +845,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
+            if (((e / 2) & 1) && e / 4 < STG_COLS / GROUPS / 8 && fuse) drain_step(e / 4);
           }
         }
         // The barrier below closes the reads of the p2c staging rows of this key tile (so the next tile's band can
