@@ -74,6 +74,11 @@ constexpr uint32_t OFF_LX = OFF_CUR + 160;          // row-sum partials of a fin
 constexpr uint32_t OFF_MX = OFF_LX + 2 * GROUPS * BQ * 4;   // its reference exponents, [item parity][row]
 constexpr uint32_t OFF_PERM = OFF_MX + 2 * BQ * 4;          // padded form: sequences by decreasing length
 constexpr int PERM_MAX = 256;
+#ifndef TDB_FCB
+#define TDB_FCB 9
+#endif
+constexpr int FCB = TDB_FCB;                    // step of the exponential loop at which the fused c2p drain starts
+static_assert(FCB >= 0 && FCB + STG_COLS / GROUPS / 8 <= KPT / 2 - 1, "the fused drain's last step must lie inside the loop");
 constexpr uint32_t SMEM_BYTES = OFF_PERM + PERM_MAX * 2 + 1024;   // + slack for the 1024-byte alignment of the base
 static_assert(OFF_STP % 16 == 0 && OFF_XCH % 16 == 0 && OFF_BAR % 16 == 0 && OFF_LX % 16 == 0, "offsets must stay 16-byte aligned");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -537,9 +542,11 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_commit(bar(V_EMPTY));
       };
 
-      // Issue order: C(0) S(0) P2(0) C(1) | S(1) P2(1) C(2) PV(0) | S(2) P2(2) C(3) PV(1) | ...  so that the band of
-      // tile g+2 is under way as soon as the band buffer has been drained of tile g+1, well before the CUDA warps
-      // ask for it, and P.V of tile g never delays the scores of the tiles after it.
+      // Issue order: C(0) S(0) P2(0) C(1) | S(1) P2(1) PV(0) C(2) | S(2) P2(2) PV(1) C(3) | ...  While the CUDA warps
+      // work on tile g they enable, in this order: C(g+1) (the p2c band of tile g leaves the band buffer during the
+      // c2p phase), P2(g+1) (the c2p band of tile g+1 leaves it during the exponentials) and P.V(g); the lane waits
+      // idle at the two band products, which are the tile's critical chain, and fits S(g+1) - enabled long before -
+      // between them.
       TileCur cc, cs, cv;                  // c2p stream (two tiles ahead), score/p2c stream (one ahead), P.V stream
       cc.n = 0; cc.it = 0; cur_fetch(cc);
       cs = cc; cv = cc;
@@ -554,9 +561,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           if (nx.ok) {
             cs = nx;
             issue_s(cs, gs); issue_p2(cs, gs); ++gs;
-            if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
           }
           issue_pv(cv, gv++);
+          if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
           if (cv.it + 1 == cv.n_kv) release(cv.n);
           cur_next(cv);
           if (!cv.ok) break;
@@ -709,10 +716,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     switch_item(0);
     if (cur.n_kv > 0) {
       if (tid == 0) leader_publish(2);
-      {                                                                // bands of the very first key tile
+      {                                                                // c2p band of the very first key tile
         const bool sat0 = LONG && tile_saturated(p, cur.q0, 0);
         drain_c(sat0);
-        drain_p2(sat0);
         bar_all_cuda_warps();
       }
       float m_run = 0.f, l_part = 0.f;
@@ -728,6 +734,37 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         // loop's steps: that loop is bound by the special-function unit and has issue slots to spare, and the
         // tensor-memory loads' latency disappears behind it); saturated tiles keep the separate one-value drain.
         const bool fuse = C2P && has_next && !sat && !sat_n;
+        // Likewise this tile's own p2c band is drained inside the c2p loop just below (it was issued as soon as the c2p
+        // band of this tile had been drained, during the tile before).
+        const bool fuse_p = C2P && P2C && !sat;
+        uint32_t dr[8];
+        auto drain_begin = [&](uint32_t src) {
+          wait(BAND_FULL, (uint32_t)(drains & 1));
+          ++drains;
+          tc_fence_after();
+          tmem_ld8(src, dr);
+        };
+        // step c (0..4) of a fused drain: store the eight columns that have arrived, ask for the next eight; the band
+        // buffer is handed back as soon as the last load has completed
+        auto drain_step = [&](int c, uint32_t src, uint32_t dst) {
+          tmem_ld_wait8(dr);
+          sts_128(dst + 16u * (uint32_t)c, pack_bf16x2(__uint_as_float(dr[0]), __uint_as_float(dr[1])),
+                  pack_bf16x2(__uint_as_float(dr[2]), __uint_as_float(dr[3])),
+                  pack_bf16x2(__uint_as_float(dr[4]), __uint_as_float(dr[5])),
+                  pack_bf16x2(__uint_as_float(dr[6]), __uint_as_float(dr[7])));
+          if (c + 1 < STG_COLS / GROUPS / 8) {
+            tmem_ld8(src + 8u * (uint32_t)(c + 1), dr);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAND_FREE));
+          }
+        };
+        const uint32_t dc_src = tmem + lane_base + TM_RING + (uint32_t)(32 * qd + (STG_COLS / GROUPS) * grp);
+        const uint32_t dc_dst = c_row + 2u * (uint32_t)((STG_COLS / GROUPS) * grp);
+        const uint32_t dp_src = tmem + lane_base + TM_RING + (uint32_t)(96 - 32 * qd + (STG_COLS / GROUPS) * grp);
+        const uint32_t dp_dst = p_row + 2u * (uint32_t)((STG_COLS / GROUPS) * grp);
+        if (fuse_p) drain_begin(dp_src);
         wait(S_FULL, (uint32_t)(g & 1));
         tc_fence_after();
         float s[KPT];
@@ -759,42 +796,24 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
               asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(v));
               s[KPT - 1 - 2 * k] = add_bf16(s[KPT - 1 - 2 * k], lo);
               s[KPT - 2 - 2 * k] = add_bf16(s[KPT - 2 - 2 * k], hi);
+              if ((k & 1) && k / 2 < STG_COLS / GROUPS / 8 && fuse_p) drain_step(k / 2, dp_src, dp_dst);
             }
           }
-          bar_quadrant(qd);
-          if (has_next && !fuse) drain_c(sat_n);
         }
+        if (P2C && !fuse_p) drain_p2(sat);
+        // Closes the reads of the c2p staging rows (the next tile's band is drained into them during phase 2) and
+        // completes the p2c staging rows, which phase 2 reads across quadrants.
+        bar_all_cuda_warps();
+        // The copy of the item two ahead goes into the slot of the item two back, whose last reader (that item's
+        // epilogue, inside the first tile of the item before this one) lies behind the barrier above.
+        if (tid == 0 && it == 0 && n > 0) leader_publish(n + 2);
         // Phase 2.  Scores stay unscaled in s[]; the exponentials are taken at once against the reference exponent
         // of the previous tiles (0 on the first tile) so that the MUFU work overlaps the shared-memory reads, and
         // are redone only for rows whose new maximum is more than 2^8 above (or, on the first tile, 2^64 below) it.
         const float m_prev = (it > 0) ? m_run : 0.f;
         float lsum = 0.f;
         uint32_t pk[KPT / 2];
-        uint32_t dr[8];
-        const uint32_t d_src = tmem + lane_base + TM_RING + (uint32_t)(32 * qd + (STG_COLS / GROUPS) * grp);
-        const uint32_t d_dst = c_row + 2u * (uint32_t)((STG_COLS / GROUPS) * grp);
-        if (fuse) {
-          wait(BAND_FULL, (uint32_t)(drains & 1));
-          ++drains;
-          tc_fence_after();
-          tmem_ld8(d_src, dr);
-        }
-        // step c (0..4) of the fused drain: store the eight columns that have arrived, ask for the next eight; the
-        // band buffer is handed back as soon as the last load has completed
-        auto drain_step = [&](int c) {
-          tmem_ld_wait8(dr);
-          sts_128(d_dst + 16u * (uint32_t)c, pack_bf16x2(__uint_as_float(dr[0]), __uint_as_float(dr[1])),
-                  pack_bf16x2(__uint_as_float(dr[2]), __uint_as_float(dr[3])),
-                  pack_bf16x2(__uint_as_float(dr[4]), __uint_as_float(dr[5])),
-                  pack_bf16x2(__uint_as_float(dr[6]), __uint_as_float(dr[7])));
-          if (c + 1 < STG_COLS / GROUPS / 8) {
-            tmem_ld8(d_src + 8u * (uint32_t)(c + 1), dr);
-          } else {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(BAND_FREE));
-          }
-        };
+        if (C2P && has_next && !fuse) drain_c(sat_n);
         if (sat) {
           // Saturated tile: p2c is one value per key (floats at the start of the p2c staging area); masking is
           // applied unconditionally, this path is not the common one.
@@ -829,7 +848,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
-            if (((e / 2) & 1) && e / 4 < STG_COLS / GROUPS / 8 && fuse) drain_step(e / 4);
+            if (fuse && e / 2 == FCB) drain_begin(dc_src);
+            if (fuse && e / 2 > FCB && e / 2 <= FCB + STG_COLS / GROUPS / 8) drain_step(e / 2 - FCB - 1, dc_src, dc_dst);
           }
         } else {
 #pragma unroll
@@ -845,7 +865,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
-            if (((e / 2) & 1) && e / 4 < STG_COLS / GROUPS / 8 && fuse) drain_step(e / 4);
+            if (fuse && e / 2 == FCB) drain_begin(dc_src);
+            if (fuse && e / 2 > FCB && e / 2 <= FCB + STG_COLS / GROUPS / 8) drain_step(e / 2 - FCB - 1, dc_src, dc_dst);
           }
         }
         // The barrier below closes the reads of the p2c staging rows of this key tile (so the next tile's band can
@@ -912,20 +933,18 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_READY));
-        if (has_next) drain_p2(sat_n);                                 // p2c staging rows are free since the barrier above
         if (last_of_item) {                                            // what the item's epilogue needs from this thread
           sts_f32(lx_mine + (uint32_t)(n & 1) * (GROUPS * BQ * 4), l_part);
           if (grp == 0) sts_f32(mx_row + (uint32_t)(n & 1) * (BQ * 4), m_run);
         }
-        bar_all_cuda_warps();                                          // next tile's staging complete; exchange buffer free
         ++g;
         if (!last_of_item) { ++it; continue; }
         ++n;
         it = 0;
         switch_item(n);
         if (cur.n_kv <= 0) break;
-        if (tid == 0) leader_publish(n + 2);
       }
+      bar_all_cuda_warps();                                            // the last tile's row sums are in shared memory
       finish_item(n - 1, g - 1);
     }
   }
