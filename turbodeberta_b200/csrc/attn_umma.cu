@@ -204,6 +204,11 @@ template <int N> __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, co
   }
 }
 
+// Four 32-bit columns of this thread's tensor-memory lane (asynchronous: tmem_st_wait() before anybody is told).
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // Move 32 fp32 columns of this thread's tensor-memory lane to 32 bf16 of a staging row.
 __device__ __forceinline__ void drain_chunk(uint32_t taddr, uint32_t dst_saddr) {
   uint32_t r[32];
@@ -814,6 +819,12 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         float lsum = 0.f;
         uint32_t pk[KPT / 2];
         if (C2P && has_next && !fuse) drain_c(sat_n);
+        // P of this tile goes to tensor memory while it is being formed, eight keys at a time, so the P.V product of
+        // the tile before must have finished with the buffer (it has, long ago: it was issued when that tile ended).
+        if (g > 0) {
+          wait(O_FULL, (uint32_t)((g - 1) & 1));
+          tc_fence_after();
+        }
         if (sat) {
           // Saturated tile: p2c is one value per key (floats at the start of the p2c staging area); masking is
           // applied unconditionally, this path is not the common one.
@@ -836,6 +847,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
           }
+          tmem_st_cols<KPT / 2>(tP, pk);
         } else if (nvalid >= KPT) {
 #pragma unroll
           for (int e = 0; e < KPT; e += 2) {
@@ -848,6 +860,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
+            if ((e / 2) % 4 == 3) tmem_st4(tP + (uint32_t)(e / 2 - 3), pk[e / 2 - 3], pk[e / 2 - 2], pk[e / 2 - 1], pk[e / 2]);
             if (fuse && e / 2 == FCB) drain_begin(dc_src);
             if (fuse && e / 2 > FCB && e / 2 <= FCB + STG_COLS / GROUPS / 8) drain_step(e / 2 - FCB - 1, dc_src, dc_dst);
           }
@@ -865,6 +878,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             const float a = ex2(fmaf(x0, sl2, -m_prev)), b = ex2(fmaf(x1, sl2, -m_prev));
             lsum += a + b;
             pk[e / 2] = pack_bf16x2(a, b);
+            if ((e / 2) % 4 == 3) tmem_st4(tP + (uint32_t)(e / 2 - 3), pk[e / 2 - 3], pk[e / 2 - 2], pk[e / 2 - 1], pk[e / 2]);
             if (fuse && e / 2 == FCB) drain_begin(dc_src);
             if (fuse && e / 2 > FCB && e / 2 <= FCB + STG_COLS / GROUPS / 8) drain_step(e / 2 - FCB - 1, dc_src, dc_dst);
           }
@@ -888,9 +902,13 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           const float row_max = mx * sl2;                              // sl2 > 0
           const float excess = row_max - m_prev;
           const bool redo = (excess > 8.f) || (it == 0 && excess < -64.f);
-          if (redo) {
-            m_new = row_max;
-            alpha = ex2(m_prev - m_new);
+          if (__any_sync(0xffffffffu, redo)) {
+            // The store to tensor memory is a warp-wide instruction, so the whole warp forms its P again (rows that
+            // keep their exponent get the same values as before) and overwrites what the loop stored.
+            if (redo) {
+              m_new = row_max;
+              alpha = ex2(m_prev - m_new);
+            }
             lsum = 0.f;
 #pragma unroll
             for (int e = 0; e < KPT; e += 2) {
@@ -898,11 +916,11 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
               lsum += a + b;
               pk[e / 2] = pack_bf16x2(a, b);
             }
+            tmem_st_wait();
+            tmem_st_cols<KPT / 2>(tP, pk);
           }
         }
         if (it > 0) {
-          wait(O_FULL, (uint32_t)((g - 1) & 1));
-          tc_fence_after();
           if (moved && __any_sync(0xffffffffu, alpha != 1.f)) {
             uint32_t r[OPT];
             tmem_ld_cols<OPT>(tO, r);
@@ -928,7 +946,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         }
         l_part = (it > 0 ? l_part * alpha : 0.f) + lsum;
         m_run = m_new;
-        tmem_st_cols<KPT / 2>(tP, pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
