@@ -547,31 +547,31 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         tc_commit(bar(V_EMPTY));
       };
 
-      // Issue order: C(0) S(0) P2(0) C(1) | S(1) P2(1) PV(0) C(2) | S(2) P2(2) PV(1) C(3) | ...  While the CUDA warps
-      // work on tile g they enable, in this order: C(g+1) (the p2c band of tile g leaves the band buffer during the
-      // c2p phase), P2(g+1) (the c2p band of tile g+1 leaves it during the exponentials) and P.V(g); the lane waits
-      // idle at the two band products, which are the tile's critical chain, and fits S(g+1) - enabled long before -
-      // between them.
+      // Issue order, by rounds r = -1, 0, 1, ...:  S(r) P2(r) PV(r-1) C(r+1), i.e.
+      //   C(0) | S(0) P2(0) C(1) | S(1) P2(1) PV(0) C(2) | S(2) P2(2) PV(1) C(3) | ...
+      // While the CUDA warps work on tile g they enable, in this order: C(g+1) (the p2c band of tile g leaves the band
+      // buffer during the c2p phase), P2(g+1) (the c2p band of tile g+1 leaves it during the exponentials) and
+      // P.V(g); the lane waits idle at the two band products, which are the tile's critical chain, and fits S(g+1) -
+      // enabled long before - between them.  One loop with every product issued from a single place keeps the lane's
+      // code small (it runs once per tile and should not fall out of the instruction cache in between).
       TileCur cc, cs, cv;                  // c2p stream (two tiles ahead), score/p2c stream (one ahead), P.V stream
       cc.n = 0; cc.it = 0; cur_fetch(cc);
       cs = cc; cv = cc;
       int gc = 0, gs = 0, gv = 0;
       if (cv.ok) {
-        if (C2P) { issue_c(cc, gc++); cur_next(cc); }
-        issue_s(cs, gs); issue_p2(cs, gs); ++gs;
-        if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
-        while (true) {
-          TileCur nx = cs;
-          cur_next(nx);
-          if (nx.ok) {
-            cs = nx;
+#pragma unroll 1
+        for (int r = -1; ; ++r) {
+          if (r >= 0 && cs.ok) {
             issue_s(cs, gs); issue_p2(cs, gs); ++gs;
+            cur_next(cs);
           }
-          issue_pv(cv, gv++);
+          if (r > 0) {
+            issue_pv(cv, gv++);
+            if (cv.it + 1 == cv.n_kv) release(cv.n);
+            cur_next(cv);
+            if (!cv.ok) break;
+          }
           if (C2P && cc.ok) { issue_c(cc, gc++); cur_next(cc); }
-          if (cv.it + 1 == cv.n_kv) release(cv.n);
-          cur_next(cv);
-          if (!cv.ok) break;
         }
       }
       release(cv.n);                       // the end-of-stream marker
