@@ -23,14 +23,21 @@
 // that consist of padded rows only; in the padded form it hands the sequences out longest first, so that the items
 // with the most key tiles are not the ones that finish last).
 //
-// Pipeline: the MMA lane issues C(0) S(0) P2(0) C(1) | S(g+1) P2(g+1) C(g+2) PV(g) | ..., so the bands and scores
-// of the next key tiles are produced while the CUDA warps work on tile g; C and P2 of a tile pass through the one
-// band buffer in tensor memory (one full/free barrier pair), each drained to its staging rows - 40 columns per
-// warp - before the other is issued.  The CUDA warps walk one flat stream of key tiles across work items: per
-// tile they add the c2p term, drain C of the next tile, add the p2c term and take the exponentials against the
-// reference exponent of the tiles before (a voting barrier tells whether any row has to move it), store P and
-// drain P2 of the next tile.  The epilogue of an item (O / l, staged in shared memory so that whole 128-byte rows
-// are stored) runs inside the first tile of the next item, where the wait for its last P.V product costs nothing.
+// Pipeline: the MMA lane issues C(0) | S(0) P2(0) C(1) | S(1) P2(1) PV(0) C(2) | ..., so the bands and scores of the
+// next key tile are produced while the CUDA warps work on tile g; C and P2 pass through the one band buffer in tensor
+// memory (one full/free barrier pair), each drained to its staging rows - 40 columns per warp - before the other is
+// issued.  The CUDA warps walk one flat stream of key tiles across work items with two CTA-wide barriers per tile:
+//   phase 1  add the c2p term (skewed 32-bit reads of the thread's own staging row); between the steps of that loop the
+//            warp drains its share of THIS tile's p2c band, eight columns at a time (which frees the band buffer for
+//            the next tile's c2p band)                                                        -> barrier
+//   phase 2  add the p2c term and take the exponentials against the reference exponent of the tiles before; P goes to
+//            tensor memory eight keys at a time as it is formed; in the second half of the loop the warp drains its
+//            share of the NEXT tile's c2p band the same way                                   -> voting barrier
+//   then     only if some row has to move its exponent: exchange maxima, form P again, rescale O; announce P.
+// Fusing the drains into the two loops hides the tensor-memory load latency behind arithmetic that has issue slots to
+// spare, and leaves each band product a whole phase of the CUDA warps to complete in.
+// The epilogue of an item (O / l, staged in shared memory so that whole 128-byte rows are stored) runs inside the first
+// tile of the next item, where the wait for its last P.V product costs nothing.
 // All hand-offs are mbarriers with bounded waits; a wait that gives up sets a CTA-wide abort flag and the status
 // word, after which every role runs out its loops without waiting (the CUDA warps take their trip counts from
 // one copy of the work items kept by thread 0, so their named barriers still match), tensor memory is freed, and
@@ -818,7 +825,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
         const float m_prev = (it > 0) ? m_run : 0.f;
         float lsum = 0.f;
         uint32_t pk[KPT / 2];
-        if (C2P && has_next && !fuse) drain_c(sat_n);
         // P of this tile goes to tensor memory while it is being formed, eight keys at a time, so the P.V product of
         // the tile before must have finished with the buffer (it has, long ago: it was issued when that tile ended).
         if (g > 0) {
@@ -883,6 +889,9 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
             if (fuse && e / 2 > FCB && e / 2 <= FCB + STG_COLS / GROUPS / 8) drain_step(e / 2 - FCB - 1, dc_src, dc_dst);
           }
         }
+        // Tiles around a saturated one drain the next c2p band here, in one piece (the band product was issued when
+        // this tile's p2c band left the buffer, at the top of the tile, and needs about this long).
+        if (C2P && has_next && !fuse) drain_c(sat_n);
         // The barrier below closes the reads of the p2c staging rows of this key tile (so the next tile's band can
         // be drained into them) and carries a vote: only when some thread of the CTA saw a score far from the
         // reference exponent do the rows exchange their maxima and move the exponent; otherwise it simply stays.
