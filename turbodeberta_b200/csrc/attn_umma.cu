@@ -233,14 +233,16 @@ __device__ __forceinline__ void drain_chunk(uint32_t taddr, uint32_t dst_saddr) 
 
 // One unit of work: a 128-query tile of one sequence for one head.
 // A 128x128 score tile whose distances q - k all lie at or beyond the saturation distance (on one side): every
-// score of the tile uses the same table row, so c2p is one value per query row and p2c one value per key, and the
-// position bands shrink from 256 columns to the 16-column minimum of the MMA.
+// score of the tile uses the same table row r, so c2p is Q[i].Kr[r] and p2c is K[j].Qr[r].  The expanded tables repeat
+// that row over their whole saturated end, so a 128-row box from there is a tile of identical rows, and both terms are
+// folded into the score product itself:  S = Q.K^T + Q.KrRep^T + QrRep.K^T  (three accumulating products into the
+// same accumulator).  Such a tile has no band products, no drains and no gathers at all.
 __device__ __forceinline__ bool tile_saturated(const AttnParams& p, int q0, int k0) {
   const int sat = p.exp_delta_max - TDB_EXPAND_MARGIN;
   const int d = q0 - k0;
   return (d - (BK - 1) >= sat) || (d + (BQ - 1) <= -sat);
 }
-constexpr int SATN = 16;
+constexpr int SATN = 128;                       // rows of the repeated-row boxes
 
 struct Work {
   int q0, len, rows, bcoord, h, n_kv;      // n_kv == 0: tile of padded query rows only (zeros, no tensor work)
@@ -472,7 +474,6 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     if (lane == 0) {
       constexpr uint32_t ID_S = make_idesc_bf16(128, BK, 0);
       constexpr uint32_t ID_BAND = make_idesc_bf16(128, BAND, 0);
-      constexpr uint32_t ID_SAT = make_idesc_bf16(128, SATN, 0);
       constexpr uint32_t ID_PV = make_idesc_bf16(128, HD, 1);
       const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
       const uint64_t dKr = smem_desc_sw128(sKr), dQr = smem_desc_sw128(sQr);
@@ -504,38 +505,52 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
       };
       // content->position band of key tile g (global count): one 256-column product into the band buffer
       auto issue_c = [&](const TileCur& c, int g) {
+        if (LONG && tile_saturated(p, c.q0, c.it * BK)) return;          // folded into the score product
         wait(KR_FULL, (uint32_t)(g & 1));
         wait_q(c);
         wait_ring_free();
         tc_fence_after();
         const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
-        const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dQc + 2 * k, dKr + 2 * k, idesc, k > 0);
+        for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dQc + 2 * k, dKr + 2 * k, ID_BAND, k > 0);
         ring_filled();
         tc_commit(bar(KR_EMPTY));
       };
       // content score of key tile g; the last one of an item releases the item's Q buffer
       auto issue_s = [&](const TileCur& c, int g) {
+        const bool sat = LONG && tile_saturated(p, c.q0, c.it * BK);
         wait(K_FULL, (uint32_t)(g & 1));
-        if (!C2P) wait_q(c);
+        wait_q(c);
+        if (sat && C2P) wait(KR_FULL, (uint32_t)(g & 1));
+        if (sat && P2C) wait(QR_FULL, (uint32_t)(g & 1));
         if (g > 0) wait(S_TAKEN, (uint32_t)((g - 1) & 1));
         tc_fence_after();
         const uint64_t dQc = dQ + (uint64_t)((c.n & 1) * ((BQ * HD * 2) >> 4));
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQc + 2 * k, dK + 2 * k, ID_S, k > 0);
+        if (sat) {                           // the two position terms of a saturated tile: repeated-row operands
+          if (C2P) {
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQc + 2 * k, dKr + 2 * k, ID_S, 1u);
+            tc_commit(bar(KR_EMPTY));
+          }
+          if (P2C) {
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k) mma_ss(tS, dQr + 2 * k, dK + 2 * k, ID_S, 1u);
+            tc_commit(bar(QR_EMPTY));
+          }
+        }
         tc_commit(bar(S_FULL));
         if (c.it + 1 == c.n_kv) tc_commit(bar(Q_EMPTY + (c.n & 1)));
       };
       // position->content band of key tile g (rows = keys), once the c2p band has been drained; releases K
       auto issue_p2 = [&](const TileCur& c, int g) {
-        if (P2C) {
+        if (P2C && !(LONG && tile_saturated(p, c.q0, c.it * BK))) {
           wait(QR_FULL, (uint32_t)(g & 1));
           wait_ring_free();
           tc_fence_after();
-          const uint32_t idesc = (LONG && tile_saturated(p, c.q0, c.it * BK)) ? ID_SAT : ID_BAND;
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dK + 2 * k, dQr + 2 * k, idesc, k > 0);
+          for (int k = 0; k < HD / 16; ++k) mma_ss(tBand, dK + 2 * k, dQr + 2 * k, ID_BAND, k > 0);
           ring_filled();
           tc_commit(bar(QR_EMPTY));
         }
@@ -609,36 +624,29 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
 
     // Drain the band buffer into this warp's share of the staging rows.  kind 0: c2p (window starts at 32*qd),
     // kind 1: p2c (96 - 32*qd).
-    auto drain_band = [&](int kind, bool sat) {
+    auto drain_band = [&](int kind) {
       wait(BAND_FULL, (uint32_t)(drains & 1));
       ++drains;
       tc_fence_after();
-      if (sat) {                                                       // one value per row: column 0 of the band
-        if (grp == 0) {
-          uint32_t r[16];
-          tmem_ld_cols<16>(tmem + lane_base + TM_RING, r);
-          sts_f32(kind == 0 ? c_row : stP + 4u * (uint32_t)row_t, __uint_as_float(r[0]));
-        }
-      } else {
-        // The 160 staged columns of a row are split evenly over the four warps that own the row: 40 columns each.
-        const int local = (STG_COLS / GROUPS) * grp;                   // position inside the staging row
-        const uint32_t src = tmem + lane_base + TM_RING + (uint32_t)((kind == 0 ? 32 * qd : 96 - 32 * qd) + local);
-        const uint32_t dst = (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local;
-        drain_chunk(src, dst);
-        uint32_t r[8];
-        tmem_ld8(src + 32, r);
-        tmem_ld_wait8(r);
-        sts_128(dst + 64, pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
-                pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
-                pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
-                pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
-      }
+      // The 160 staged columns of a row are split evenly over the four warps that own the row: 40 columns each.
+      const int local = (STG_COLS / GROUPS) * grp;                     // position inside the staging row
+      const uint32_t src = tmem + lane_base + TM_RING + (uint32_t)((kind == 0 ? 32 * qd : 96 - 32 * qd) + local);
+      const uint32_t dst = (kind == 0 ? c_row : p_row) + 2u * (uint32_t)local;
+      drain_chunk(src, dst);
+      uint32_t r[8];
+      tmem_ld8(src + 32, r);
+      tmem_ld_wait8(r);
+      sts_128(dst + 64, pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+              pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+              pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+              pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAND_FREE));
     };
-    auto drain_c = [&](bool sat) { if (C2P) drain_band(0, sat); };
-    auto drain_p2 = [&](bool sat) { if (P2C) drain_band(1, sat); };
+    // Saturated tiles have no bands (their position terms are part of the score product).
+    auto drain_c = [&](bool sat) { if (C2P && !sat) drain_band(0); };
+    auto drain_p2 = [&](bool sat) { if (P2C && !sat) drain_band(1); };
 
     // The CUDA-core warps walk one flat stream of key tiles.  Thread 0 copies the work items from the scheduler's
     // ring into four slots, two items ahead of the one being processed, so that every warp takes its trip counts
@@ -792,9 +800,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           // The 32 values sit at descending addresses from c_read; read them as 17 aligned 32-bit words and
           // realign odd lanes with a funnel shift (half the shared-memory wavefronts of 16-bit loads).
           if (sat) {
-            const float cq = lds_f32(c_row);
-#pragma unroll
-            for (int e = 0; e < KPT; ++e) s[e] += cq;
+            // nothing to add: the score product of a saturated tile already holds all three terms
           } else {
             const uint32_t lo_addr = (c_read - 2u * (KPT - 1)) & ~3u;
             const uint32_t sh = (uint32_t)(lane & 1) * 16u;
@@ -832,18 +838,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
           tc_fence_after();
         }
         if (sat) {
-          // Saturated tile: p2c is one value per key (floats at the start of the p2c staging area); masking is
-          // applied unconditionally, this path is not the common one.
-          if (P2C) {
-#pragma unroll
-            for (int v = 0; v < KPT / 4; ++v) {
-              float4 t;
-              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                           : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w)
-                           : "r"(stP + 4u * (uint32_t)(KPT * grp + 4 * v)));
-              s[4 * v] += t.x; s[4 * v + 1] += t.y; s[4 * v + 2] += t.z; s[4 * v + 3] += t.w;
-            }
-          }
+          // Saturated tile: the scores are complete; masking is applied unconditionally (not the common path).
 #pragma unroll
           for (int e = 0; e < KPT; e += 2) {
             const float x0 = (e < nvalid) ? s[e] : -CUDART_INF_F;
