@@ -13,7 +13,9 @@
 // needs are the contiguous window win = [q0 - k0 - 127 + exp_delta_max, +256), one TMA box.  The diagonal
 // read C[i][i-j+127] cannot be done from registers (the column depends on the lane), so both bands are
 // drained from tensor memory to shared memory as bf16 rows and read back skewed.  Tiles whose distances are all
-// saturated need one value per query row / per key instead of a band (long-sequence variant of the kernel).
+// saturated (long-sequence variant of the kernel) use one table row for every score, and the tables repeat that row
+// over their saturated ends, so both position terms become two more products into the score accumulator itself
+// (operands = 128-row boxes of identical rows): such tiles have no band, no drain and no gather.
 //
 // Warp roles (608 threads): warps 0-15 do the CUDA-core work; warp w owns tensor-memory lanes 32*(w%4)..+31
 // (query rows, or key rows of P2) and column group w/4, i.e. four threads share a query row and each handles 32
@@ -752,7 +754,8 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
                                                   : tile_saturated(p, item_slots[(n + 1) & 3].q0, 0));
         // The next tile's c2p band is drained inside this tile's exponential loop (eight columns at a time between the
         // loop's steps: that loop is bound by the special-function unit and has issue slots to spare, and the
-        // tensor-memory loads' latency disappears behind it); saturated tiles keep the separate one-value drain.
+        // tensor-memory loads' latency disappears behind it); a saturated tile has no band, and the tile before or after
+        // one drains in one piece instead.
         const bool fuse = C2P && has_next && !sat && !sat_n;
         // Likewise this tile's own p2c band is drained inside the c2p loop just below (it was issued as soon as the c2p
         // band of this tile had been drained, during the tile before).
