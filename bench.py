@@ -29,9 +29,9 @@ sys.path.insert(0, ROOT)
 METRIC = "disentangled_attn_algorithmic_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the attention kernel, from an ncu capture of that
-# workload, as summarised in profiles/ (c2: 56.43 MB read + 4.28 MB written; c3: 419.9 + 105.5 MB; c5f: 79.9 + 10.7 MB).
+# workload, as summarised in profiles/ (c2: 56.31 MB read + 3.54..3.96 MB written; c3: 420.3 + 106.9 MB; c5f: 80.3 + 11.2 MB).
 # Workloads without a capture report null.
-NCU_TRAFFIC_BYTES = {"c2": 60.71e6, "c3": 525.4e6, "c5f": 90.68e6}
+NCU_TRAFFIC_BYTES = {"c2": 60.06e6, "c3": 527.2e6, "c5f": 91.47e6}
 NO_TRAFFIC_REASON = "no ncu capture of this workload (a launch holds more than the capture-size rule allows or was not captured)"
 
 
