@@ -323,6 +323,35 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TM_COLS);
     tmem_relinquish();
   }
+  // Padded form with lengths: the items of long sequences cost more (one key tile per 128 valid keys), so the
+  // sequences are handed out by decreasing number of key tiles - a counting sort that every CTA's scheduler warp
+  // repeats for itself (a few hundred warp instructions; skipped for batches where it would cost more).  It runs
+  // while the other warps set the CTA up: it needs nothing but the lengths in global memory and its own corner of
+  // shared memory.
+  const uint16_t* perm = nullptr;
+  if (warp == NCW + 2) {
+    const int qtiles = (p.L + BQ - 1) / BQ;
+    if (!p.varlen && p.seqlens && p.n_seqs > 1 && p.n_seqs <= PERM_MAX && p.n_seqs * (qtiles + 1) <= 2048) {
+      uint16_t* pw = reinterpret_cast<uint16_t*>(gbase + OFF_PERM);
+      int base = 0;
+      for (int b = qtiles; b >= 0; --b) {
+        for (int s0 = 0; s0 < p.n_seqs; s0 += 32) {
+          const int sq = s0 + lane;
+          int key = -1;
+          if (sq < p.n_seqs) {
+            int len = p.seqlens[sq];
+            len = len < 0 ? 0 : (len > p.L ? p.L : len);
+            key = (len + BK - 1) / BK;
+          }
+          const uint32_t m = __ballot_sync(0xffffffffu, key == b);
+          if (key == b) pw[base + __popc(m & ((1u << lane) - 1u))] = (uint16_t)sq;
+          base += __popc(m);
+        }
+      }
+      __syncwarp();
+      perm = pw;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -411,33 +440,7 @@ attn_umma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tm_q, c
     // padded query rows only (padded form) are zeroed here by the whole warp and never reach the other roles.
     // The first item of a CTA is its own index (no round trip to the counter before the pipeline can start); the
     // counter hands out the items after those.
-    // Padded form with lengths: the items of long sequences cost more (one key tile per 128 valid keys), so the
-    // sequences are handed out by decreasing number of key tiles - a counting sort that every CTA's scheduler warp
-    // repeats for itself (a few hundred warp instructions; skipped for batches where it would cost more).
-    const uint16_t* perm = nullptr;
-    {
-      const int qtiles = (p.L + BQ - 1) / BQ;
-      if (!p.varlen && p.seqlens && p.n_seqs > 1 && p.n_seqs <= PERM_MAX && p.n_seqs * (qtiles + 1) <= 2048) {
-        uint16_t* pw = reinterpret_cast<uint16_t*>(gbase + OFF_PERM);
-        int base = 0;
-        for (int b = qtiles; b >= 0; --b) {
-          for (int s0 = 0; s0 < p.n_seqs; s0 += 32) {
-            const int sq = s0 + lane;
-            int key = -1;
-            if (sq < p.n_seqs) {
-              int len = p.seqlens[sq];
-              len = len < 0 ? 0 : (len > p.L ? p.L : len);
-              key = (len + BK - 1) / BK;
-            }
-            const uint32_t m = __ballot_sync(0xffffffffu, key == b);
-            if (key == b) pw[base + __popc(m & ((1u << lane) - 1u))] = (uint16_t)sq;
-            base += __popc(m);
-          }
-        }
-        __syncwarp();
-        perm = pw;
-      }
-    }
+    // Padded form with lengths: the sequences are handed out in the order sorted above.
     int n = 0;
     bool first = true;
     while (true) {
