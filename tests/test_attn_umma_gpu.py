@@ -261,3 +261,41 @@ def test_padding_of_k_and_v_may_hold_anything():
         assert torch.equal(clean, dirty)
     ref = util.oracle_fixed(q, k, v, tables, w.lengths, w, True, True, scale)
     util.assert_close(run(kd, vd, UMMA), ref, DT, "dirty padding")
+
+
+def test_long_padded_batch_mixes_band_tiles_saturated_tiles_and_dirty_padding():
+    """A padded batch long enough for saturated key tiles (all distances of a 128 x 128 tile beyond the bucket table's
+    span: their position terms ride in the score product) next to ordinary band tiles, with ragged lengths - so that
+    saturated runs start and end inside items, last key tiles are partial, and whole query tiles are padding - and
+    with NaN in the padding of K and V.  Valid rows must match the oracle; padded rows are zeros."""
+    from turbodeberta_b200.ops.flash_attention import flash_attention_with_disentangled
+    lengths = [1536, 1100, 641, 130]
+    w = _wl(lengths, 1536)
+    q, k, v, rel, P = util.device_inputs(w, DT)
+    tables = util.make_tables(w, rel, P)
+    lens = torch.as_tensor(np.asarray(w.lengths), dtype=torch.int32, device="cuda")
+    scale = 1.0 / (3 * 64) ** 0.5
+    kd, vd = k.clone(), v.clone()
+    for b, n in enumerate(lengths):
+        kd[b, n:] = float("nan")
+        vd[b, n:] = float("nan")
+    out = flash_attention_with_disentangled(
+        q.permute(0, 2, 1, 3), kd.permute(0, 2, 1, 3), vd.permute(0, 2, 1, 3), None, None, False, scale, 256, 512,
+        seqlens=lens, tables=tables, kernel=UMMA).permute(0, 2, 1, 3)
+    assert torch.isfinite(out.float()).all()
+    for b, n in enumerate(lengths):
+        assert torch.count_nonzero(out[b, n:]).item() == 0
+    ref = util.oracle_fixed(q, k, v, tables, w.lengths, w, True, True, scale)
+    util.assert_close(out, ref, DT, "long padded batch")
+    simt = flash_attention_with_disentangled(
+        q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), None, None, False, scale, 256, 512,
+        seqlens=lens, tables=tables, kernel=SIMT).permute(0, 2, 1, 3)
+    assert (out.float() - simt.float()).abs().max().item() < 1e-2
+
+
+@pytest.mark.parametrize("c2p,p2c", [(True, False), (False, True)])
+def test_long_sequences_with_one_position_term(c2p, p2c):
+    """The long-sequence instantiations with a single position term: saturated tiles fold only that term into the
+    score product, band tiles drain only that band."""
+    o, ref = _fixed(_wl([1408, 700], 1408, hidden=64, heads=1), c2p=c2p, p2c=p2c)
+    util.assert_close(o, ref, DT, f"long sequences, c2p={c2p}, p2c={p2c}")
