@@ -99,7 +99,8 @@ enum Bar { Q_FULL = 0 /* Q_FULL + buffer */, Q_FULL1, Q_EMPTY /* Q_EMPTY + buffe
            S_FULL, S_TAKEN, BAND_FULL, BAND_FREE, P_READY, O_FULL,
            DONE, WORK_FULL0, WORK_FULL1, WORK_FULL2, WORK_FULL3,
            WORK_EMPTY0, WORK_EMPTY1, WORK_EMPTY2, WORK_EMPTY3, NBARS };
-constexpr int WORK_RING = 4;
+constexpr int WORK_RING = 3;                     // the item in progress and the two after it: what the roles look ahead, and
+                                                // no more (every item claimed early is taken from a CTA that may be free sooner)
 constexpr int WORK_READERS = 3 + 1 + 1;         // three producer lanes, the MMA lane, the CUDA-core warps' leader
 static_assert(NBARS * 8 <= 256, "barrier block");
 
