@@ -21,7 +21,7 @@
 // (query rows, or key rows of P2) and column group w/4, i.e. four threads share a query row and each handles 32
 // of the 128 keys, which puts four warps on every scheduler to hide latency.  Warp 16 = TMA producers (lane 0:
 // tables and K, lane 1: V, lane 2: Q), warp 17 = tensor-memory allocation + MMA issue (one lane), warp 18 =
-// scheduler (draws work items from a device-wide counter, publishes them in a shared-memory ring, zeroes tiles
+// scheduler (draws work items from a device-wide counter, publishes them in a shared-memory ring of three, zeroes tiles
 // that consist of padded rows only; in the padded form it hands the sequences out longest first, so that the items
 // with the most key tiles are not the ones that finish last).
 //
